@@ -75,7 +75,9 @@ def _ensure_registered() -> None:
 def architecture_for(config_dict: dict[str, Any]) -> Architecture:
     """The architecture entry that a config.json (as a dict) names."""
     _ensure_registered()
-    names = config_dict.get("architectures") or []
+    names = list(config_dict.get("architectures") or [])
+    if isinstance(config_dict.get("architecture"), str):  # some checkpoints name one architecture, as a string
+        names.append(config_dict["architecture"])
     for name in names:
         if name in ARCHITECTURES:
             return ARCHITECTURES[name]

@@ -74,3 +74,65 @@ TS_EXPORT int ts_feed_tokens(int* ids, const int* source, const int* lanes, cons
   if (n <= 0) return 0;
   return ts_launch(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, ids, (const int*)source, lanes, rows, n);
 }
+
+// A second table added to the embedding rows: row hash(token before, token) of a table of
+// `buckets` hashed rows and one more row, which the first token of a sequence takes (it has no
+// token before it):  hidden[t] += table[(prev * mul_prev + id * mul_cur) mod buckets].
+// The token before the first token of a step's portion is the last token of the portion before,
+// kept per request in `last_token[state_slots[b]]`; the thread that reads it for a portion's first
+// token also writes the portion's last token there, so no other thread touches that word.
+template <typename TW>
+__global__ void pair_hash_embed_kernel(float* __restrict__ hidden, const TW* __restrict__ table, const int* __restrict__ ids,
+                                       const int* __restrict__ positions, const int* __restrict__ seq_index,
+                                       const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+                                       int* __restrict__ last_token, int H, int V, unsigned long long buckets,
+                                       unsigned long long mul_prev, unsigned long long mul_cur) {
+  ts_pdl_prologue();
+  __shared__ long long row_s;
+  const int t = blockIdx.x;
+  const int b = seq_index[t];
+  if (b < 0) return;  // a padded lane
+  const int id = ids[t];
+  if (threadIdx.x == 0) {
+    const int first = cu_seqlens[b];
+    int* word = last_token + state_slots[b];
+    long long row = -1;
+    if (id >= 0 && id < V) {
+      if (positions[t] == 0) {
+        row = (long long)buckets;
+      } else {
+        const int prev = (t == first) ? *word : ids[t - 1];
+        if (prev >= 0 && prev < V) row = (long long)(((unsigned long long)prev * mul_prev + (unsigned long long)id * mul_cur) % buckets);
+      }
+    }
+    if (t == first) *word = ids[cu_seqlens[b + 1] - 1];
+    row_s = row;
+  }
+  __syncthreads();
+  const long long row = row_s;
+  float* dst = hidden + (size_t)t * H;
+  if (row < 0) {  // a token id outside the vocabulary: loud, as in the gather
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const TW* src = table + (size_t)row * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] += ts_to_float(src[i]);
+}
+
+TS_EXPORT int ts_pair_hash_embed(float* hidden, const void* table, int table_dtype, const int* ids, const int* positions,
+                                 const int* seq_index, const int* cu_seqlens, const int* state_slots, int* last_token, int T, int H,
+                                 int V, long long buckets, long long mul_prev, long long mul_cur, void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || V <= 0 || buckets <= 0 || mul_prev < 0 || mul_cur < 0) return TS_ERR_BAD_ARGUMENT;
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (table_dtype == TS_DTYPE_F32)
+    return ts_launch(pair_hash_embed_kernel<float>, dim3(T), dim3(threads), 0, s, hidden, (const float*)table, ids, positions, seq_index,
+                     cu_seqlens, state_slots, last_token, H, V, (unsigned long long)buckets, (unsigned long long)mul_prev,
+                     (unsigned long long)mul_cur);
+  if (table_dtype == TS_DTYPE_BF16)
+    return ts_launch(pair_hash_embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, hidden, (const __nv_bfloat16*)table, ids,
+                     positions, seq_index, cu_seqlens, state_slots, last_token, H, V, (unsigned long long)buckets,
+                     (unsigned long long)mul_prev, (unsigned long long)mul_cur);
+  return TS_ERR_BAD_ARGUMENT;
+}

@@ -1,0 +1,308 @@
+// A feed-forward of routed experts, for any sizes and both element types, without a trip to the
+// host: every grid is sized from the step's token count alone.
+//
+//   router_topk : per token, from float32 router logits: score = sigmoid(logit), the `top` largest
+//                 scores (the lower index wins a tie) with their experts; the scores are handed on
+//                 as they are, or divided by their sum (`renormalize`).
+//   moe_plan    : the (token, choice) pairs sorted by expert: offsets[e] .. offsets[e+1] are expert
+//                 e's places in `order` (pair indices), tile_offsets[e] its first row tile.
+//   moe_gate_up : for the pairs of each expert, rows x[token] * weight(pair) times the expert's gate
+//                 and up matrices, then a = min(g, limit), b = clamp(u, -limit, limit),
+//                 act = a * sigmoid(alpha a) * (b + 1)           -> act[place, I]
+//   moe_down    : act[place] times the expert's down matrix       -> pair_out[pair, N]
+//   moe_combine : out[t] = sum over the token's pairs (each times its weight, if weights are given)
+//                 (+ shared[t]), summed in float32 in the order of the choices.
+//
+// The two products are FFMA tiles of 64 x 64 with float32 sums over k in increasing order: a
+// pair's result does not depend on its place inside its expert's rows, so the order in which the
+// plan happens to list an expert's pairs changes nothing.
+#include "common.cuh"
+
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 16
+#define MOE_MAX_EXPERTS 4096
+
+__global__ void router_topk_kernel(const float* __restrict__ logits, int T, int E, int top, int renormalize, int* __restrict__ ids,
+                                   float* __restrict__ weights) {
+  ts_pdl_prologue();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  const float* z = logits + (size_t)warp * E;
+  int* my_ids = ids + (size_t)warp * top;
+  float* my_w = weights + (size_t)warp * top;
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= (my_ids[j] == e);
+      const float v = z[e];
+      if (!taken && (v > best || (v == best && e < best_e))) {
+        best = v;
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ov > best || (ov == best && oe < best_e)) {
+        best = ov;
+        best_e = oe;
+      }
+    }
+    const float score = 1.f / (1.f + expf(-best));
+    total += score;
+    if (lane == 0) {
+      my_ids[k] = best_e < E ? best_e : 0;
+      my_w[k] = score;
+    }
+    __syncwarp();
+  }
+  if (renormalize && lane == 0)
+    for (int k = 0; k < top; ++k) my_w[k] /= total;
+}
+
+TS_EXPORT int ts_router_topk(const float* logits, int T, int E, int top, int renormalize, int* ids, float* weights, void* stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
+  return ts_launch(router_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, T, E, top, renormalize, ids, weights);
+}
+
+// One block: counts per expert, their prefix sums, then every pair takes the next place of its expert.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ offsets, int* __restrict__ tile_offsets,
+                                int* __restrict__ order) {
+  ts_pdl_prologue();
+  extern __shared__ int sm[];
+  int* count = sm;           // [E]
+  int* cursor = sm + E;      // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = rows;
+      tile_offsets[e] = tiles;
+      cursor[e] = rows;
+      rows += count[e];
+      tiles += (count[e] + MOE_BM - 1) / MOE_BM;
+    }
+    offsets[E] = rows;
+    tile_offsets[E] = tiles;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) order[atomicAdd(&cursor[e], 1)] = i;
+  }
+}
+
+TS_EXPORT int ts_moe_plan(const int* ids, int P, int E, int* offsets, int* tile_offsets, int* order, void* stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > MOE_MAX_EXPERTS) return TS_ERR_UNSUPPORTED_SIZE;
+  return ts_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, ids, P, E, offsets, tile_offsets, order);
+}
+
+// Which expert a row tile belongs to: the last e with tile_offsets[e] <= tile.
+__device__ __forceinline__ int moe_tile_expert(const int* __restrict__ tile_offsets, int E, int tile) {
+  int lo = 0, hi = E;  // invariant: tile_offsets[lo] <= tile < tile_offsets[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_offsets[mid] <= tile) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256) moe_gate_up_kernel(const TA* __restrict__ x, const float* __restrict__ pair_weight,
+                                                          const int* __restrict__ order, const int* __restrict__ offsets,
+                                                          const int* __restrict__ tile_offsets, const TA* __restrict__ gate,
+                                                          const TA* __restrict__ up, TA* __restrict__ act, int E, int K, int I, int top,
+                                                          float limit, float alpha) {
+  ts_pdl_prologue();
+  __shared__ float As[MOE_BK][MOE_BM + 1];
+  __shared__ float Gs[MOE_BK][MOE_BN + 1];
+  __shared__ float Us[MOE_BK][MOE_BN + 1];
+  __shared__ int src_row[MOE_BM];
+  __shared__ float src_scale[MOE_BM];
+  const int tile = blockIdx.y;
+  if (tile >= tile_offsets[E]) return;
+  const int e = moe_tile_expert(tile_offsets, E, tile);
+  const int row0 = offsets[e] + (tile - tile_offsets[e]) * MOE_BM, row_end = offsets[e + 1];
+  const int n0 = blockIdx.x * MOE_BN;
+  for (int r = threadIdx.x; r < MOE_BM; r += 256) {
+    const int place = row0 + r;
+    const int pair = place < row_end ? order[place] : -1;
+    src_row[r] = pair < 0 ? -1 : pair / top;
+    src_scale[r] = pair < 0 ? 0.f : pair_weight[pair];
+  }
+  __syncthreads();
+  const TA* G = gate + (size_t)e * I * K;
+  const TA* U = up + (size_t)e * I * K;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float accg[4][4] = {}, accu[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+    for (int i = threadIdx.x; i < MOE_BM * MOE_BK; i += 256) {
+      const int r = i / MOE_BK, c = i % MOE_BK;
+      const int gk = k0 + c, gn = n0 + r, sr = src_row[r];
+      As[c][r] = (sr >= 0 && gk < K) ? ts_to_float(x[(size_t)sr * K + gk]) * src_scale[r] : 0.f;
+      const bool w_ok = gn < I && gk < K;
+      Gs[c][r] = w_ok ? ts_to_float(G[(size_t)gn * K + gk]) : 0.f;
+      Us[c][r] = w_ok ? ts_to_float(U[(size_t)gn * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_BK; ++k) {
+      float a[4], g[4], u[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        g[j] = Gs[k][tx * 4 + j];
+        u[j] = Us[k][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          accg[i][j] = fmaf(a[i], g[j], accg[i][j]);
+          accu[i][j] = fmaf(a[i], u[j], accu[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int place = row0 + ty * 4 + i;
+    if (place >= row_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= I) continue;
+      // the sums are rounded to the element type first, as a product stored to memory would be
+      const float gv = ts_to_float(ts_from_float<TA>(accg[i][j])), uv = ts_to_float(ts_from_float<TA>(accu[i][j]));
+      const float a = fminf(gv, limit);
+      const float b = fminf(fmaxf(uv, -limit), limit);
+      act[(size_t)place * I + gn] = ts_from_float<TA>(a / (1.f + expf(-alpha * a)) * (b + 1.f));
+    }
+  }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256) moe_down_kernel(const TA* __restrict__ act, const int* __restrict__ order,
+                                                       const int* __restrict__ offsets, const int* __restrict__ tile_offsets,
+                                                       const TA* __restrict__ down, TA* __restrict__ pair_out, int E, int I, int N) {
+  ts_pdl_prologue();
+  __shared__ float As[MOE_BK][MOE_BM + 1];
+  __shared__ float Ws[MOE_BK][MOE_BN + 1];
+  const int tile = blockIdx.y;
+  if (tile >= tile_offsets[E]) return;
+  const int e = moe_tile_expert(tile_offsets, E, tile);
+  const int row0 = offsets[e] + (tile - tile_offsets[e]) * MOE_BM, row_end = offsets[e + 1];
+  const int n0 = blockIdx.x * MOE_BN;
+  const TA* W = down + (size_t)e * N * I;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < I; k0 += MOE_BK) {
+    for (int i = threadIdx.x; i < MOE_BM * MOE_BK; i += 256) {
+      const int r = i / MOE_BK, c = i % MOE_BK;
+      const int gk = k0 + c, gn = n0 + r, place = row0 + r;
+      As[c][r] = (place < row_end && gk < I) ? ts_to_float(act[(size_t)place * I + gk]) : 0.f;
+      Ws[c][r] = (gn < N && gk < I) ? ts_to_float(W[(size_t)gn * I + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_BK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int place = row0 + ty * 4 + i;
+    if (place >= row_end) continue;
+    const size_t pair = (size_t)order[place];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) pair_out[pair * N + gn] = ts_from_float<TA>(acc[i][j]);
+    }
+  }
+}
+
+TS_EXPORT int ts_moe_gate_up(const void* x, int act_dtype, const float* pair_weight, const int* order, const int* offsets,
+                             const int* tile_offsets, const void* gate, const void* up, void* act, int P, int E, int K, int I, int top,
+                             float limit, float alpha, void* stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || K <= 0 || I <= 0 || top <= 0) return TS_ERR_BAD_ARGUMENT;
+  const dim3 grid((I + MOE_BN - 1) / MOE_BN, (P + MOE_BM - 1) / MOE_BM + E);
+  if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32)
+    return ts_launch(moe_gate_up_kernel<float>, grid, dim3(256), 0, s, (const float*)x, pair_weight, order, offsets, tile_offsets,
+                     (const float*)gate, (const float*)up, (float*)act, E, K, I, top, limit, alpha);
+  if (act_dtype == TS_DTYPE_BF16)
+    return ts_launch(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, pair_weight, order, offsets,
+                     tile_offsets, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)act, E, K, I, top, limit, alpha);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+TS_EXPORT int ts_moe_down(const void* act, int act_dtype, const int* order, const int* offsets, const int* tile_offsets, const void* down,
+                          void* pair_out, int P, int E, int I, int N, void* stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || I <= 0 || N <= 0) return TS_ERR_BAD_ARGUMENT;
+  const dim3 grid((N + MOE_BN - 1) / MOE_BN, (P + MOE_BM - 1) / MOE_BM + E);
+  if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32)
+    return ts_launch(moe_down_kernel<float>, grid, dim3(256), 0, s, (const float*)act, order, offsets, tile_offsets, (const float*)down,
+                     (float*)pair_out, E, I, N);
+  if (act_dtype == TS_DTYPE_BF16)
+    return ts_launch(moe_down_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)act, order, offsets, tile_offsets,
+                     (const __nv_bfloat16*)down, (__nv_bfloat16*)pair_out, E, I, N);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+template <typename TA>
+__global__ void moe_combine_kernel(const TA* __restrict__ pair_out, const TA* __restrict__ shared, TA* __restrict__ out,
+                                   const float* __restrict__ pair_weight, int N, int top, size_t total) {
+  ts_pdl_prologue();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / N;
+  const int n = (int)(idx - t * N);
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) sum += ts_to_float(pair_out[(t * top + k) * N + n]) * (pair_weight ? pair_weight[t * top + k] : 1.f);
+  if (shared) sum += ts_to_float(shared[idx]);
+  out[idx] = ts_from_float<TA>(sum);
+}
+
+TS_EXPORT int ts_moe_combine(const void* pair_out, const void* shared, void* out, const float* pair_weight, int act_dtype, int T, int N,
+                             int top, void* stream) {
+  if (T <= 0) return 0;
+  if (N <= 0 || top <= 0) return TS_ERR_BAD_ARGUMENT;
+  const size_t total = (size_t)T * N;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32)
+    return ts_launch(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)pair_out, (const float*)shared, (float*)out, pair_weight, N, top, total);
+  if (act_dtype == TS_DTYPE_BF16)
+    return ts_launch(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)pair_out,
+                     (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, pair_weight, N, top, total);
+  return TS_ERR_BAD_ARGUMENT;
+}

@@ -155,3 +155,65 @@ TS_EXPORT int ts_residual_add(float* hidden, const void* delta, int act_dtype, l
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();
 }
+
+// The norm on a branch's output, for layers that norm what a sublayer returns instead of what it
+// reads:  hidden[row] += branch[row] * rsqrt(mean(branch[row]^2) + eps) * weight, all in float32,
+// and, if asked for, the new row once more in the compute type (what the next sublayer reads).
+template <typename TB, typename TO>
+__global__ void rmsnorm_add_kernel(const TB* __restrict__ branch, const float* __restrict__ weight, float* __restrict__ hidden,
+                                   TO* __restrict__ rounded, int H, float eps) {
+  ts_pdl_prologue();
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const TB* b = branch + (size_t)row * H;
+  float* h = hidden + (size_t)row * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = ts_to_float(b[i]);
+    ss += v * v;
+  }
+  ss = ts_block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = h[i] + ts_to_float(b[i]) * rstd * weight[i];
+    h[i] = v;
+    if (rounded) rounded[(size_t)row * H + i] = ts_from_float<TO>(v);
+  }
+}
+
+TS_EXPORT int ts_rmsnorm_add(const void* branch, int branch_dtype, const float* weight, float* hidden, void* rounded, int rounded_dtype,
+                             int rows, int H, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0) return TS_ERR_BAD_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
+  if (branch_dtype == TS_DTYPE_F32 && (rounded == nullptr || rounded_dtype == TS_DTYPE_F32))
+    return ts_launch(rmsnorm_add_kernel<float, float>, dim3(rows), dim3(threads), 0, s, (const float*)branch, weight, hidden, (float*)rounded, H, eps);
+  if (branch_dtype == TS_DTYPE_F32 && rounded_dtype == TS_DTYPE_BF16)
+    return ts_launch(rmsnorm_add_kernel<float, __nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (const float*)branch, weight, hidden, (__nv_bfloat16*)rounded, H, eps);
+  if (branch_dtype == TS_DTYPE_BF16 && (rounded == nullptr || rounded_dtype == TS_DTYPE_BF16))
+    return ts_launch(rmsnorm_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (const __nv_bfloat16*)branch, weight, hidden, (__nv_bfloat16*)rounded, H, eps);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+// out = rows in another element type (what a sublayer that reads the residual stream itself is
+// handed when nothing before it has produced the rounded rows; or rounded rows widened again).
+template <typename TI, typename TO>
+__global__ void round_rows_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  ts_pdl_prologue();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = ts_from_float<TO>(ts_to_float(in[i]));
+}
+
+TS_EXPORT int ts_round_rows(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream) {
+  if (n <= 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (in_dtype == TS_DTYPE_F32 && out_dtype == TS_DTYPE_BF16)
+    return ts_launch(round_rows_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const float*)in, (__nv_bfloat16*)out, (size_t)n);
+  if (in_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_F32)
+    return ts_launch(round_rows_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)in, (float*)out, (size_t)n);
+  if (in_dtype == TS_DTYPE_F32 && out_dtype == TS_DTYPE_F32)
+    return ts_launch(round_rows_kernel<float, float>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n);
+  return TS_ERR_BAD_ARGUMENT;
+}

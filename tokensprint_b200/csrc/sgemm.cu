@@ -14,8 +14,12 @@
 __global__ void __launch_bounds__(256) sgemm_nt_kernel(const float* __restrict__ A,
                                                        const float* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K,
-                                                       long long lda, long long ldw, long long ldc) {
+                                                       long long lda, long long ldw, long long ldc,
+                                                       long long batch_a, long long batch_w, long long batch_c) {
   ts_pdl_prologue();
+  A += (size_t)blockIdx.z * batch_a;  // product blockIdx.z of a batch of equal shapes
+  W += (size_t)blockIdx.z * batch_w;
+  C += (size_t)blockIdx.z * batch_c;
   __shared__ float As[SG_BK][SG_BM + 1];
   __shared__ float Ws[SG_BK][SG_BN + 1];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -61,5 +65,16 @@ TS_EXPORT int ts_sgemm_nt(const float* A, const float* W, float* C, int M, int N
   if (K <= 0 || lda < K || ldw < K || ldc < N) return TS_ERR_BAD_ARGUMENT;
   dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(sgemm_nt_kernel, grid, dim3(256), 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldw, ldc);
+  return ts_launch(sgemm_nt_kernel, grid, dim3(256), 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldw, ldc, 0LL, 0LL, 0LL);
+}
+
+// `batch` products of one shape: product b reads A + b * batch_a and W + b * batch_w and writes
+// C + b * batch_c (elements); the rows of each may be strided (lda, ldw, ldc).
+TS_EXPORT int ts_sgemm_nt_batched(const float* A, const float* W, float* C, int M, int N, int K, long long lda, long long ldw,
+                                  long long ldc, int batch, long long batch_a, long long batch_w, long long batch_c, void* stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || lda < K || ldw < K || ldc < N) return TS_ERR_BAD_ARGUMENT;
+  dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM, batch);
+  if (grid.y > 65535 || batch > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  return ts_launch(sgemm_nt_kernel, grid, dim3(256), 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
 }

@@ -165,7 +165,7 @@ class ModelRunner:
         self.layer_caches = [
             self.cache_tensors.layer_cache(self.model.run_cache[i], run.writes_cache)
             for i, run in enumerate(self.model.spec.run_order)
-        ]
+        ] + [self.cache_tensors.layer_cache(c, True) for c in getattr(self.model, "extra_caches", [])]
 
     # -- sizing ---------------------------------------------------------------------
 

@@ -10,7 +10,7 @@ import torch
 import tokensprint_b200.parts  # noqa: F401  (registers the built-in parts)
 from tokensprint_b200 import ops
 from tokensprint_b200.models.spec import ModelSpec
-from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, PreNormed, StepContext, TensorSpec, build_part
+from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, PreNormed, Rounded, StepContext, TensorSpec, build_part
 from tokensprint_b200.parts.linear import folding_possible, linear_float32_out, linear_scaled
 from tokensprint_b200.weights.loader import LoadedTensors, WeightSource, check_tensors
 
@@ -71,6 +71,17 @@ class Model:
             if (need.group_key, need.k_row, need.v_row, need.state_shape) != (w.group_key, w.k_row, w.v_row, w.state_shape):
                 raise ValueError(f"run {i} and run {plan[c].writer_run} share a cache but need different ones")
         self.cache_plan: list[CachePlanEntry] = [p for p in plan if p is not None]
+        # An embedding transform that keeps something per request between steps gets a cache of its
+        # own behind the runs' caches (writer_run -1: no run fills it); whoever binds device memory
+        # hands forward() one LayerCache per run and then one per entry of `extra_caches`.
+        self.extra_caches: list[int] = []
+        self._embedding_cache: Optional[int] = None
+        if self.embedding_transform is not None:
+            need = self.embedding_transform.cache_need()
+            if need.kind != "none" or need.state_shape is not None:
+                self.cache_plan.append(CachePlanEntry(need, -1))
+                self._embedding_cache = len(spec.run_order) + len(self.extra_caches)
+                self.extra_caches.append(len(self.cache_plan) - 1)
 
     # -- weights --------------------------------------------------------------
 
@@ -123,7 +134,10 @@ class Model:
         hidden = torch.empty((T, self.spec.hidden_size), device=self.device, dtype=torch.float32)
         ops.embed_gather(hidden, self.embedding, step.token_ids)
         if self.embedding_transform is not None:
-            hidden = self.embedding_transform.forward(hidden, step)
+            if self._embedding_cache is not None:
+                hidden = self.embedding_transform.forward(hidden, step, cache=caches[self._embedding_cache])
+            else:
+                hidden = self.embedding_transform.forward(hidden, step)
         pending = None
         order = self.spec.run_order
         # the final norm may be prepared by the last block when every row's logits are wanted
@@ -160,6 +174,8 @@ class Model:
         return out
 
     def _head_product(self, hidden: torch.Tensor, pending, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
+        if isinstance(pending, Rounded):
+            pending = None  # `hidden` is complete
         if isinstance(pending, PreNormed):
             if num_rows == hidden.shape[0] and folding_possible(num_rows, self.dtype, self.head):
                 return linear_scaled(pending, self.head, float32_out=True)

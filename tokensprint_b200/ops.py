@@ -39,6 +39,24 @@ _SIGNATURES = {
     ],
     "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "ts_sgemm_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
+    "ts_sgemm_nt_batched": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
+    "ts_pair_hash_embed": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                           _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
+    "ts_rmsnorm_add": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "ts_round_rows": [_c_void_p, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "ts_latent_prepare": [_c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float,
+                          _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_latent_attention_simple": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+    "ts_gelu_tanh": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "ts_capped_glu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
+    "ts_gelu_gate_rows": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_void_p],
+    "ts_router_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "ts_moe_plan": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "ts_moe_gate_up": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_float, _c_float, _c_void_p],
+    "ts_moe_down": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
 }
 
 _functions: dict[str, object] = {}
@@ -444,6 +462,285 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"sgemm_nt: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _check("sgemm_nt", _fn("ts_sgemm_nt")(
         a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), w.stride(0), out.stride(0), _stream()))
+
+
+def sgemm_nt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = a[b] @ w[b]^T in true float32 for b < batch: a [batch, M, K], w [batch, N, K], out
+    [batch, M, N], each possibly a strided view (unit inner stride)."""
+    flush_gemm_chain()
+    for name, t in (("a", a), ("w", w), ("out", out)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 3 or t.stride(2) != 1:
+            raise KernelError(f"sgemm_nt_batched: {name} must be a float32 CUDA tensor [batch, rows, cols] with unit inner stride")
+    batch, M, K = a.shape
+    N = w.shape[1]
+    if w.shape != (batch, N, K) or out.shape != (batch, M, N):
+        raise KernelError(f"sgemm_nt_batched: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check("sgemm_nt_batched", _fn("ts_sgemm_nt_batched")(
+        a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(1), w.stride(1), out.stride(1), batch,
+        a.stride(0), w.stride(0), out.stride(0), _stream()))
+
+
+def library_bmm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = a[b] @ w[b]^T by the library's batched GEMM (bfloat16, float32 sums): the many small
+    per-head products of a latent attention layer.  Strided views are taken as they are."""
+    flush_gemm_chain()
+    torch.bmm(a, w.transpose(1, 2), out=out)
+
+
+def pair_hash_embed(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, seq_index: torch.Tensor,
+                    cu_seqlens: torch.Tensor, state_slots: torch.Tensor, last_token: torch.Tensor, buckets: int, mul_prev: int,
+                    mul_cur: int, vocab: int) -> None:
+    """hidden[t] += table[(token before * mul_prev + token * mul_cur) mod buckets]; a sequence's first
+    token takes row `buckets`.  The token before a portion's first token comes from `last_token`
+    [slots] i32 (one word per request's state slot), which then takes the portion's last token."""
+    flush_gemm_chain()
+    _cuda_contig("hidden", hidden, torch.float32)
+    _cuda_contig("table", table)
+    for name, t in (("ids", ids), ("positions", positions), ("seq_index", seq_index), ("cu_seqlens", cu_seqlens),
+                    ("state_slots", state_slots), ("last_token", last_token)):
+        _cuda_contig(name, t, torch.int32)
+    T, H = hidden.shape
+    if table.shape != (buckets + 1, H):
+        raise KernelError(f"pair_hash_embed: the table must be [{buckets + 1}, {H}], got {tuple(table.shape)}")
+    if min(ids.numel(), positions.numel(), seq_index.numel()) < T:
+        raise KernelError("pair_hash_embed: ids, positions and seq_index need one entry per token")
+    _check("pair_hash_embed", _fn("ts_pair_hash_embed")(
+        hidden.data_ptr(), table.data_ptr(), _act_code("table", table), ids.data_ptr(), positions.data_ptr(), seq_index.data_ptr(),
+        cu_seqlens.data_ptr(), state_slots.data_ptr(), last_token.data_ptr(), T, H, int(vocab), int(buckets), int(mul_prev),
+        int(mul_cur), _stream()))
+
+
+def rmsnorm_add(branch: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor, eps: float, rounded: Optional[torch.Tensor] = None) -> None:
+    """hidden += branch * rsqrt(mean(branch^2) + eps) * weight in float32 (the norm sits on the
+    branch's output); `rounded`, if given, takes the new rows of hidden in its own element type."""
+    flush_gemm_chain()
+    _cuda_contig("branch", branch)
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("hidden", hidden, torch.float32)
+    T, H = hidden.shape
+    if branch.shape != hidden.shape or weight.numel() != H:
+        raise KernelError(f"rmsnorm_add: shapes disagree: branch {tuple(branch.shape)}, hidden {tuple(hidden.shape)}, weight {tuple(weight.shape)}")
+    code = 0
+    if rounded is not None:
+        _cuda_contig("rounded", rounded)
+        if rounded.shape != hidden.shape:
+            raise KernelError("rmsnorm_add: rounded must have hidden's shape")
+        code = _act_code("rounded", rounded)
+    _check("rmsnorm_add", _fn("ts_rmsnorm_add")(
+        branch.data_ptr(), _act_code("branch", branch), weight.data_ptr(), hidden.data_ptr(), _ptr(rounded), code, T, H, float(eps), _stream()))
+
+
+def round_rows(rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out = rows in out's element type (float32 -> bfloat16 rounds; bfloat16 -> float32 widens)."""
+    flush_gemm_chain()
+    _cuda_contig("rows", rows)
+    _cuda_contig("out", out)
+    if out.shape != rows.shape:
+        raise KernelError("round_rows: shapes disagree")
+    _check("round_rows", _fn("ts_round_rows")(rows.data_ptr(), _act_code("rows", rows), out.data_ptr(), _act_code("out", out), rows.numel(), _stream()))
+
+
+ROTARY_PAIRINGS = {"half": 0, "neighbours": 1}
+LATENT_SIMPLE_MAX_KEY_DIM = 1024
+
+
+def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gate_off: int, q_abs: torch.Tensor, cache: Optional[torch.Tensor],
+                   slot_mapping: Optional[torch.Tensor], positions: torch.Tensor, latent_weight: torch.Tensor, eps: float,
+                   inv_freq: Optional[torch.Tensor], rot_dims: int, pairing: str, gates: Optional[torch.Tensor], num_heads: int,
+                   nope_dim: int, rot_dim: int, rank: int) -> None:
+    """What follows the stacked projection of a latent attention layer, per token: the latent (columns
+    kv_off .. kv_off+rank of `proj`) RMS-normed with `latent_weight`, the key part behind it and
+    every head's rotated query part turned by the token's position, [latent ; key part] stored in
+    `cache` [slots, rank+rot] at slot_mapping[t] (-1 or no mapping: not stored), the rotated query
+    parts written to q_abs[t, head, rank:], and gates[t, head] = sigmoid(proj[t, gate_off+head])."""
+    flush_gemm_chain()
+    _cuda_contig("proj", proj)
+    _cuda_contig("q_abs", q_abs, proj.dtype)
+    _cuda_contig("positions", positions, torch.int32)
+    _cuda_contig("latent_weight", latent_weight, torch.float32)
+    T, ld = proj.shape
+    H, dn, dr = num_heads, nope_dim, rot_dim
+    if q_abs.numel() != T * H * (rank + dr):
+        raise KernelError(f"latent_prepare: q_abs must hold [{T}, {H}, {rank + dr}], got {tuple(q_abs.shape)}")
+    if q_off + H * (dn + dr) > ld or kv_off + rank + dr > ld or (gates is not None and gate_off + H > ld):
+        raise KernelError("latent_prepare: the column ranges do not fit the projection's width")
+    if slot_mapping is not None:
+        if cache is None:
+            raise KernelError("latent_prepare: a slot mapping needs the cache")
+        _cuda_contig("cache", cache, proj.dtype)
+        _cuda_contig("slot_mapping", slot_mapping, torch.int32)
+        if cache.shape[-1] != rank + dr or slot_mapping.numel() < T:
+            raise KernelError(f"latent_prepare: cache rows must be {rank + dr} wide and slot_mapping hold {T} entries")
+    if gates is not None:
+        _cuda_contig("gates", gates, torch.float32)
+        if gates.numel() != T * H:
+            raise KernelError("latent_prepare: gates must be [T, heads]")
+    if rot_dims:
+        if inv_freq is None:
+            raise KernelError("latent_prepare: a rotation needs its inverse frequencies")
+        _cuda_contig("inv_freq", inv_freq, torch.float32)
+        if inv_freq.numel() != rot_dims // 2 or rot_dims > dr or rot_dims % 2:
+            raise KernelError(f"latent_prepare: {rot_dims} rotated entries of {dr} need {rot_dims // 2} frequencies")
+    _check("latent_prepare", _fn("ts_latent_prepare")(
+        proj.data_ptr(), _act_code("proj", proj), ld, int(q_off), int(kv_off), int(gate_off), q_abs.data_ptr(), _ptr(cache),
+        _ptr(slot_mapping), positions.data_ptr(), latent_weight.data_ptr(), float(eps), _ptr(inv_freq), int(rot_dims),
+        ROTARY_PAIRINGS[pairing], _ptr(gates), T, H, dn, dr, int(rank), _stream()))
+
+
+def latent_attention_simple(q_abs: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gates: Optional[torch.Tensor],
+                            positions: torch.Tensor, seq_index: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                            num_heads: int, rank: int, rot_dim: int, scale: float, window: int = 0) -> None:
+    """Causal attention of absorbed queries q_abs [T, H, rank+rot] over cached rows [pages, page,
+    rank+rot] on CUDA cores: out [T, H, rank] = softmax(q_abs . row * scale) @ row[:rank], times
+    gates[t, h] if given.  Float32 or bfloat16; scores, softmax and sums in float32."""
+    flush_gemm_chain()
+    _cuda_contig("q_abs", q_abs)
+    _cuda_contig("cache", cache, q_abs.dtype)
+    _cuda_contig("out", out, q_abs.dtype)
+    for name, t in (("positions", positions), ("seq_index", seq_index), ("block_table", block_table)):
+        _cuda_contig(name, t, torch.int32)
+    T = q_abs.shape[0]
+    H, D = num_heads, rank + rot_dim
+    if D > LATENT_SIMPLE_MAX_KEY_DIM:
+        raise KernelError(f"latent_attention_simple: rank + rotated width must be <= {LATENT_SIMPLE_MAX_KEY_DIM}, got {D}")
+    if q_abs.numel() != T * H * D or out.numel() != T * H * rank:
+        raise KernelError("latent_attention_simple: q_abs / out do not match [T, heads, rank(+rot)]")
+    if tuple(cache.shape[-2:]) != (page_size, D):
+        raise KernelError(f"latent_attention_simple: the cache must be [pages, {page_size}, {D}], got {tuple(cache.shape)}")
+    if gates is not None:
+        _cuda_contig("gates", gates, torch.float32)
+    if block_table.dim() != 2 or positions.numel() < T or seq_index.numel() < T:
+        raise KernelError("latent_attention_simple: block_table must be [B, max_blocks]; positions and seq_index need T entries")
+    _check("latent_attention_simple", _fn("ts_latent_attention_simple")(
+        q_abs.data_ptr(), cache.data_ptr(), _act_code("q_abs", q_abs), out.data_ptr(), _ptr(gates), positions.data_ptr(),
+        seq_index.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, T, H, int(rank), int(rot_dim), float(scale),
+        int(window), _stream()))
+
+
+def gelu_tanh(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = z/2 * (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) element by element (out may be x)."""
+    flush_gemm_chain()
+    _cuda_contig("x", x)
+    _cuda_contig("out", out, x.dtype)
+    if out.shape != x.shape:
+        raise KernelError("gelu_tanh: shapes disagree")
+    _check("gelu_tanh", _fn("ts_gelu_tanh")(x.data_ptr(), out.data_ptr(), _act_code("x", x), x.numel(), _stream()))
+
+
+def capped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = a * sigmoid(alpha a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit);
+    gate_up [T, 2I] holds all gates and then all ups, out [T, I]."""
+    flush_gemm_chain()
+    _cuda_contig("gate_up", gate_up)
+    _cuda_contig("out", out, gate_up.dtype)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError(f"capped_glu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    _check("capped_glu", _fn("ts_capped_glu")(gate_up.data_ptr(), out.data_ptr(), _act_code("out", out), T, I, float(limit), float(alpha), _stream()))
+
+
+def gelu_gate_rows(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int) -> None:
+    """x[t, j] = gelu_tanh(x[t, j]) * table[ids[t], col0 + j], in place.  x [T, D], table [V, >= col0 + D]."""
+    flush_gemm_chain()
+    _cuda_contig("x", x)
+    _cuda_contig("table", table, x.dtype)
+    _cuda_contig("ids", ids, torch.int32)
+    T, D = x.shape
+    if ids.numel() < T or col0 < 0 or col0 + D > table.shape[1]:
+        raise KernelError(f"gelu_gate_rows: columns {col0}..{col0 + D} of a table {tuple(table.shape)} for {T} tokens")
+    _check("gelu_gate_rows", _fn("ts_gelu_gate_rows")(
+        x.data_ptr(), table.data_ptr(), _act_code("x", x), ids.data_ptr(), T, D, table.shape[1], int(col0), table.shape[0], _stream()))
+
+
+MOE_ROW_TILE = 64
+MOE_MAX_EXPERTS = 4096
+
+
+def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Per row of float32 logits [T, E]: the `top` experts with the largest sigmoid scores into ids
+    [T, top] i32 and their scores into weights [T, top] f32 (divided by their sum if `renormalize`)."""
+    flush_gemm_chain()
+    _cuda_contig("logits", logits, torch.float32)
+    _cuda_contig("ids", ids, torch.int32)
+    _cuda_contig("weights", weights, torch.float32)
+    T, E = logits.shape
+    if not 0 < top <= E or ids.numel() != T * top or weights.numel() != T * top:
+        raise KernelError(f"router_topk: top {top} of {E} experts, ids {tuple(ids.shape)}, weights {tuple(weights.shape)}")
+    _check("router_topk", _fn("ts_router_topk")(logits.data_ptr(), T, E, int(top), int(bool(renormalize)), ids.data_ptr(), weights.data_ptr(), _stream()))
+
+
+def moe_plan(ids: torch.Tensor, num_experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sorts the (token, choice) pairs of ids [T, top] by expert on the device.  Returns offsets
+    [E+1] (expert e's places are offsets[e]..offsets[e+1]), tile_offsets [E+1] (its first row tile of
+    MOE_ROW_TILE places) and order [T*top] (place -> pair index token*top + choice)."""
+    flush_gemm_chain()
+    _cuda_contig("ids", ids, torch.int32)
+    if num_experts > MOE_MAX_EXPERTS:
+        raise KernelError(f"moe_plan: at most {MOE_MAX_EXPERTS} experts, got {num_experts}")
+    P = ids.numel()
+    plan = torch.empty(2 * (num_experts + 1) + P, dtype=torch.int32, device=ids.device)
+    offsets, tile_offsets, order = plan[: num_experts + 1], plan[num_experts + 1 : 2 * (num_experts + 1)], plan[2 * (num_experts + 1) :]
+    _check("moe_plan", _fn("ts_moe_plan")(ids.data_ptr(), P, int(num_experts), offsets.data_ptr(), tile_offsets.data_ptr(), order.data_ptr(), _stream()))
+    return offsets, tile_offsets, order
+
+
+def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple[torch.Tensor, torch.Tensor, torch.Tensor], gate: torch.Tensor,
+                up: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float) -> None:
+    """For every pair, in the plan's order: act[place] = capped_glu(gate_e (w x[token]), up_e (w x[token])).
+    x [T, K]; pair_weight [T*top] f32; gate, up [E, I, K]; act [T*top, I]."""
+    flush_gemm_chain()
+    offsets, tile_offsets, order = plan
+    _cuda_contig("x", x)
+    _cuda_contig("gate", gate, x.dtype)
+    _cuda_contig("up", up, x.dtype)
+    _cuda_contig("act", act, x.dtype)
+    _cuda_contig("pair_weight", pair_weight, torch.float32)
+    T, K = x.shape
+    E, I, K2 = gate.shape
+    P = T * top
+    if K2 != K or up.shape != gate.shape or act.shape != (P, I) or pair_weight.numel() != P or order.numel() != P:
+        raise KernelError(f"moe_gate_up: shapes disagree: x {tuple(x.shape)}, gate {tuple(gate.shape)}, up {tuple(up.shape)}, act {tuple(act.shape)}")
+    _check("moe_gate_up", _fn("ts_moe_gate_up")(
+        x.data_ptr(), _act_code("x", x), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(),
+        gate.data_ptr(), up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), _stream()))
+
+
+def moe_down(act: torch.Tensor, plan: tuple[torch.Tensor, torch.Tensor, torch.Tensor], down: torch.Tensor, pair_out: torch.Tensor) -> None:
+    """pair_out[pair] = down_e act[place] for every place of the plan.  act [P, I]; down [E, N, I]; pair_out [P, N]."""
+    flush_gemm_chain()
+    offsets, tile_offsets, order = plan
+    _cuda_contig("act", act)
+    _cuda_contig("down", down, act.dtype)
+    _cuda_contig("pair_out", pair_out, act.dtype)
+    P, I = act.shape
+    E, N, I2 = down.shape
+    if I2 != I or pair_out.shape != (P, N) or order.numel() != P:
+        raise KernelError(f"moe_down: shapes disagree: act {tuple(act.shape)}, down {tuple(down.shape)}, pair_out {tuple(pair_out.shape)}")
+    _check("moe_down", _fn("ts_moe_down")(
+        act.data_ptr(), _act_code("act", act), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), down.data_ptr(),
+        pair_out.data_ptr(), P, E, I, N, _stream()))
+
+
+def moe_combine(pair_out: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor, top: int,
+                pair_weight: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum of pair_out[t*top .. t*top+top] (each times pair_weight[pair] if given) (+ shared[t]),
+    summed in float32."""
+    flush_gemm_chain()
+    _cuda_contig("pair_out", pair_out)
+    _cuda_contig("out", out, pair_out.dtype)
+    T, N = out.shape
+    if pair_out.shape != (T * top, N):
+        raise KernelError(f"moe_combine: pair_out {tuple(pair_out.shape)} does not match out {tuple(out.shape)} with {top} choices")
+    if shared is not None:
+        _cuda_contig("shared", shared, out.dtype)
+        if shared.shape != out.shape:
+            raise KernelError("moe_combine: shared must have out's shape")
+    if pair_weight is not None:
+        _cuda_contig("pair_weight", pair_weight, torch.float32)
+        if pair_weight.numel() != T * top:
+            raise KernelError("moe_combine: one weight per pair is needed")
+    _check("moe_combine", _fn("ts_moe_combine")(pair_out.data_ptr(), _ptr(shared), out.data_ptr(), _ptr(pair_weight), _act_code("out", out),
+                                                T, N, int(top), _stream()))
 
 
 # ---------------------------------------------------------------------------
@@ -1214,7 +1511,9 @@ def library_mm(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor
 # launches; switched off, the functions are the plain ones again and nothing is paid.
 _TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_store", "attention_paged_simple",
           "sample", "sgemm_nt", "attention_paged_mma", "attention_decode_flat", "attention_prefill_tcgen05", "gemm_skinny_bf16",
-          "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm")
+          "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm", "sgemm_nt_batched", "library_bmm", "pair_hash_embed",
+          "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "gelu_tanh", "capped_glu", "gelu_gate_rows",
+          "router_topk", "moe_plan", "moe_gate_up", "moe_down", "moe_combine")
 _plain_functions: dict[str, object] = {}
 _kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
 

@@ -1,6 +1,6 @@
 """Parts of a layer.  Importing this package registers the built-in ones."""
 
-from tokensprint_b200.parts import attention, blocks, feed_forward, norms, position  # noqa: F401
+from tokensprint_b200.parts import attention, blocks, feed_forward, latent_attention, norms, position, routed, transforms  # noqa: F401
 from tokensprint_b200.parts.base import (  # noqa: F401
     BLOCKS,
     FEED_FORWARDS,

@@ -178,6 +178,15 @@ class PreNormed:
 
 
 @dataclass
+class Rounded:
+    """The rows of the (complete) residual stream once more in the compute dtype, left by the kernel
+    that last wrote them: what a block whose sublayers read the stream itself hands to the next
+    one in place of a pending branch, so that nobody has to round the rows again."""
+
+    x: torch.Tensor
+
+
+@dataclass
 class LayerCache:
     """What one run of a mixer may touch of the cache."""
 
@@ -233,6 +242,11 @@ class Norm(Part):
         """hidden (float32 residual) += delta if given; out = norm(hidden)."""
         raise NotImplementedError
 
+    def forward_branch(self, branch: torch.Tensor, hidden: torch.Tensor, rounded: Optional[torch.Tensor] = None) -> None:
+        """The norm on a sublayer's output: hidden (float32 residual) += norm(branch); `rounded`, if
+        given, takes the new rows of hidden in its own dtype (the input of the next sublayer)."""
+        raise NotImplementedError
+
 
 class PositionEncoding(Part):
     """Either hands rotary parameters to the fused kernel or rewrites q and k itself."""
@@ -266,6 +280,9 @@ class Mixer(Part):
 
 class FeedForward(Part):
     folds_norms = False  # as for Mixer
+    # True if forward() takes the keyword `residual`: the float32 rows that `x` was rounded from
+    # (a router computes its logits from them in 32-bit); a block passes it where it has them.
+    wants_residual = False
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         raise NotImplementedError
@@ -277,6 +294,11 @@ class Transform(Part):
     table) or to the logits after the head (a scale, a soft cap, a bias).  A `ModelSpec` names
     them as `embedding_transform` and `logits_transform`; the model calls them and knows
     nothing of what they do."""
+
+    def cache_need(self) -> CacheNeed:
+        """What an embedding transform keeps per request between steps (a state slot; no pages):
+        a transform that asks for one is called with the keyword `cache` (a LayerCache)."""
+        return CacheNeed()
 
     def forward(self, x: torch.Tensor, step: Optional[StepContext]) -> torch.Tensor:
         """Returns the transformed tensor (it may be `x`, changed in place).  Embedding rows:

@@ -14,6 +14,7 @@ from tokensprint_b200.parts.base import (
     PartSpec,
     PreNormed,
     ResidualNorm,
+    Rounded,
     StepContext,
     TensorSpec,
     build_part,
@@ -61,6 +62,8 @@ class PreNormBlock(Block):
         product adds into `hidden` and prepares the feed-forward's input, the feed-forward's last
         product does the same for `step.norm_after`.  Otherwise every norm is a step of its own."""
         T = hidden.shape[0]
+        if isinstance(pending, Rounded):  # the block before handed on rounded rows, no branch: nothing to add
+            pending = None
         after_block, norm_after = step.weight_after, step.norm_after
         mixer_folds = self.mixer.folds_norms and self.mixer.can_fold(T, self.dtype)
         ffn_folds = self.feed_forward.folds_norms and self.feed_forward.can_fold(T, self.dtype)
@@ -95,3 +98,79 @@ class PreNormBlock(Block):
 
     def first_weight(self):
         return self.mixer.first_weight()
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Block):
+    """h = h + Norm_a(Mixer(h)); h = h + Norm_f(FeedForward(h)); h = h + Norm_e(Extra(h)).
+
+    The norm sits on each sublayer's output and the sublayers read the residual stream itself.
+    `feed_forward` and `extra` (a second feed-forward-like sublayer, for instance a per-layer
+    token input) may each be absent.  The residual stream is float32; a sublayer reads its rows
+    rounded to the compute dtype, which the norm kernel of the sublayer before writes in the same
+    pass that adds into the stream (`Norm.forward_branch`), and the last one hands them to the
+    next block as a `Rounded`.
+    """
+
+    def __init__(self, ctx: BuildContext, *, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: Optional[PartSpec] = None,
+                 ffn_norm: Optional[PartSpec] = None, extra: Optional[PartSpec] = None, extra_norm: Optional[PartSpec] = None) -> None:
+        if (feed_forward is None) != (ffn_norm is None) or (extra is None) != (extra_norm is None):
+            raise ValueError("post_norm block: a sublayer and its norm come together")
+        self.dtype = ctx.dtype
+        self.mixer = build_part("mixer", mixer, ctx)
+        self.mixer_norm = build_part("norm", mixer_norm, ctx)
+        self.feed_forward = None if feed_forward is None else build_part("feed_forward", feed_forward, ctx)
+        self.ffn_norm = None if ffn_norm is None else build_part("norm", ffn_norm, ctx)
+        self.extra = None if extra is None else build_part("feed_forward", extra, ctx)
+        self.extra_norm = None if extra_norm is None else build_part("norm", extra_norm, ctx)
+        self._parts = tuple(p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ffn_norm, self.extra, self.extra_norm) if p is not None)
+        self.graph_safe = all(p.graph_safe for p in self._parts)
+        self.reads_through_ops = True
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [s for p in self._parts for s in p.tensor_specs()]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for p in self._parts:
+            p.load(tensors)
+
+    def first_weight(self):
+        return self.mixer.first_weight()
+
+    def _rows(self, hidden: torch.Tensor, pending) -> torch.Tensor:
+        """The stream's rows in the compute dtype: the stream itself in a float32 run, else what the
+        sublayer before left, else a rounding pass."""
+        if self.dtype == torch.float32:
+            return hidden
+        if isinstance(pending, Rounded) and pending.x.dtype == self.dtype:
+            return pending.x
+        x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+        ops.round_rows(hidden, x)
+        return x
+
+    def _add(self, norm, branch: torch.Tensor, hidden: torch.Tensor):
+        PreNormBlock._before(norm)
+        if self.dtype == torch.float32:
+            norm.forward_branch(branch, hidden)
+            return hidden
+        x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+        norm.forward_branch(branch, hidden, x)
+        return x
+
+    def forward(self, hidden, pending, step: StepContext, cache: LayerCache):
+        if isinstance(pending, torch.Tensor):  # a branch that the block before did not add
+            ops.residual_add(hidden, pending)
+            pending = None
+        x = self._rows(hidden, pending)
+        after_block = step.weight_after
+        step.weight_after = None
+        PreNormBlock._before(self.mixer)
+        x = self._add(self.mixer_norm, self.mixer.forward(x, step, cache), hidden)
+        for part, norm in ((self.feed_forward, self.ffn_norm), (self.extra, self.extra_norm)):
+            if part is None:
+                continue
+            PreNormBlock._before(part)
+            branch = part.forward(x, step, residual=hidden) if part.wants_residual else part.forward(x, step)
+            x = self._add(norm, branch, hidden)
+        step.weight_after = after_block
+        return None if self.dtype == torch.float32 else Rounded(x)

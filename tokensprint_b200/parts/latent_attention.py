@@ -1,0 +1,135 @@
+"""Latent attention over the paged cache, as a mixer part: per token the cache holds one low-rank
+latent row and one rotated key part, shared by all heads."""
+
+from __future__ import annotations
+
+from typing import Mapping, Optional
+
+import torch
+
+from tokensprint_b200 import ops
+from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, Mixer, PartSpec, StepContext, TensorSpec, build_part, register_part
+from tokensprint_b200.parts.linear import linear
+
+
+def batched_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = a[b] @ w[b]^T for a batch of small products (one per head): float32 through the
+    engine's FFMA kernel, bfloat16 through the library's batched GEMM."""
+    if a.dtype == torch.float32:
+        ops.sgemm_nt_batched(a, w, out)
+    else:
+        ops.library_bmm(a, w, out)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttentionMixer(Mixer):
+    """Attention whose keys and values are rebuilt from a latent:
+
+        q_a = [q_plain,a ; q_rot,a]          H heads of nope_dim + rot_dim query entries
+        [c ; r] = W_dkv x                    c: kv_rank entries, RMS-normed; r: rot_dim entries, rotated
+        k_a = [U_k,a c ; r],  v_a = U_v,a c  (r is the same for every head)
+        o_a = softmax(q_a . k_a * scale) v_a, times sigmoid(W_g x)_a if `gate` is named;  y = W_o [o_a]
+
+    Only [c ; r] is cached, one row of kv_rank + rot_dim entries per token in a single pool.  The
+    keys are never rebuilt: U_k,a^T q_plain,a (the absorbed query) is scored against c directly,
+    the weighted sum runs over c, and U_v,a is applied to that sum.  A step is: one product for
+    [q | c, r | gate logits], the prepare kernel (norm, rotation, store), the per-head absorbing
+    products, the attention kernel, the per-head value products, the output product.
+
+    Parameters: sizes (`hidden_size`, `num_heads`, `nope_dim`, `rot_dim`, `value_dim`, `kv_rank`),
+    `scale`, `norm_eps` of the latent's norm, `window` (0: all earlier keys), `position` (a rotary
+    spec: its width is the number of rotated entries of the rot_dim part, its pairing is honoured)
+    and the checkpoint names of the tensors.
+    """
+
+    reads_through_ops = False  # the per-head products may be the library's
+
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, num_heads: int, nope_dim: int, rot_dim: int, value_dim: int, kv_rank: int,
+                 scale: float, norm_eps: float, q: str, dkv: str, dkv_norm: str, uk: str, uv: str, o: str, gate: Optional[str] = None,
+                 window: int = 0, position: Optional[PartSpec] = None) -> None:
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.nope_dim, self.rot_dim, self.value_dim, self.kv_rank = int(nope_dim), int(rot_dim), int(value_dim), int(kv_rank)
+        self.scale, self.norm_eps, self.window = float(scale), float(norm_eps), int(window or 0)
+        if min(self.num_heads, self.kv_rank, self.value_dim) < 1 or self.nope_dim < 0 or self.rot_dim < 0 or self.nope_dim + self.rot_dim < 1:
+            raise ValueError("latent attention: heads, kv_rank and value_dim must be positive, and a head needs query entries")
+        self.names = {"q": q, "dkv": dkv, "dkv_norm": dkv_norm, "uk": uk, "uv": uv, "o": o, "gate": gate}
+        self.position = build_part("position_encoding", position, ctx) if position is not None else None
+        self.rot_dims, self.pairing = 0, "half"
+        if self.position is not None:
+            self.rot_dims, self.pairing = int(self.position.dim), self.position.pairing
+            if self.rot_dims > self.rot_dim:
+                raise ValueError(f"latent attention: {self.rot_dims} rotated entries do not fit a rotated part of {self.rot_dim}")
+        self.graph_safe = True
+        self.dtype = ctx.dtype
+        self.stacked: Optional[torch.Tensor] = None
+        self.offsets = (0, 0, 0)
+
+    @property
+    def key_dim(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.stacked
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="window" if self.window > 0 else "full", window=self.window, k_row=(self.key_dim,), single_pool=True)
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        W, H, n = self.hidden_size, self.num_heads, self.names
+        specs = [
+            TensorSpec(n["q"], (H * (self.nope_dim + self.rot_dim), W)),
+            TensorSpec(n["dkv"], (self.key_dim, W)),
+            TensorSpec(n["dkv_norm"], (self.kv_rank,), "vector"),
+            TensorSpec(n["uk"], (H * self.nope_dim, self.kv_rank)),
+            TensorSpec(n["uv"], (H * self.value_dim, self.kv_rank)),
+            TensorSpec(n["o"], (W, H * self.value_dim)),
+        ]
+        if n["gate"] is not None:
+            specs.append(TensorSpec(n["gate"], (H, W)))
+        if self.position is not None:
+            specs.extend(self.position.tensor_specs())
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n, H = self.names, self.num_heads
+        parts = [tensors[n["q"]], tensors[n["dkv"]]] + ([tensors[n["gate"]]] if n["gate"] is not None else [])
+        q_rows = parts[0].shape[0]
+        self.offsets = (0, q_rows, q_rows + self.key_dim)
+        self.stacked = torch.cat(parts, dim=0).contiguous()
+        self.latent_weight = tensors[n["dkv_norm"]]
+        # per head: U_k,a^T as a matrix [kv_rank, nope_dim] (out, in) for the absorbing product,
+        # U_v,a [value_dim, kv_rank] as it is stored
+        self.uk_t = tensors[n["uk"]].view(H, self.nope_dim, self.kv_rank).transpose(1, 2).contiguous() if self.nope_dim else None
+        self.uv = tensors[n["uv"]].view(H, self.value_dim, self.kv_rank).contiguous()
+        self.o_weight = tensors[n["o"]]
+        if self.position is not None:
+            self.position.load(tensors)
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        if cache.k_pages is None or cache.group < 0:
+            raise ops.KernelError("latent attention: this mixer needs cache pages (none were bound to its run)")
+        T, H, R, D = x.shape[0], self.num_heads, self.kv_rank, self.key_dim
+        tables = step.groups[cache.group]
+        proj = linear(x, self.stacked)
+        q_abs = torch.empty((T, H, D), device=x.device, dtype=x.dtype)
+        gates = torch.empty((T, H), device=x.device, dtype=torch.float32) if self.names["gate"] is not None else None
+        q_off, kv_off, gate_off = self.offsets
+        ops.latent_prepare(
+            proj, q_off, kv_off, gate_off, q_abs, cache.k_pages if cache.writes else None, tables.slot_mapping if cache.writes else None,
+            step.positions, self.latent_weight, self.norm_eps, None if self.position is None else self.position.frequencies(),
+            self.rot_dims, self.pairing, gates, H, self.nope_dim, self.rot_dim, R)
+        if self.nope_dim:
+            q_plain = proj[:, : H * (self.nope_dim + self.rot_dim)].view(T, H, self.nope_dim + self.rot_dim)[:, :, : self.nope_dim]
+            batched_linear(q_plain.transpose(0, 1), self.uk_t, q_abs[:, :, :R].transpose(0, 1))
+        else:
+            q_abs[:, :, :R].zero_()
+        latent_out = torch.empty((T, H, R), device=x.device, dtype=x.dtype)
+        self._attend(q_abs, latent_out, gates, step, cache, tables)
+        heads_out = torch.empty((T, H, self.value_dim), device=x.device, dtype=x.dtype)
+        batched_linear(latent_out.transpose(0, 1), self.uv, heads_out.transpose(0, 1))
+        return linear(heads_out.view(T, H * self.value_dim), self.o_weight, next_weight=step.weight_after)
+
+    def _attend(self, q_abs, out, gates, step: StepContext, cache: LayerCache, tables) -> None:
+        ops.latent_attention_simple(
+            q_abs, cache.k_pages, out, gates, step.positions, step.seq_index, tables.block_table, step.page_size, self.num_heads,
+            self.kv_rank, self.rot_dim, self.scale, self.window)

@@ -12,7 +12,9 @@ from tokensprint_b200.parts.base import NormParams, BuildContext, Norm, TensorSp
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    """y = x * rsqrt(mean(x^2) + eps) * weight, plain weight (not 1 + w), no bias.
+    """y = x * rsqrt(mean(x^2) + eps) * (offset + weight), no bias.  `offset` 0 (the default): a plain
+    weight; 1: a weight that is stored as its distance from one.  The sum offset + weight is
+    taken once, in float32, when the weight is loaded.
 
     Reference: engine/nn/base_layers.py:38-46 and engine/kernels/triton/rmsnorm.py:19-42.
     """
@@ -20,8 +22,8 @@ class RMSNorm(Norm):
     graph_safe = True
     reads_through_ops = True
 
-    def __init__(self, ctx: BuildContext, *, dim: int, eps: float, weight: str) -> None:
-        self.dim, self.eps, self.weight_name = int(dim), float(eps), weight
+    def __init__(self, ctx: BuildContext, *, dim: int, eps: float, weight: str, offset: float = 0.0) -> None:
+        self.dim, self.eps, self.weight_name, self.offset = int(dim), float(eps), weight, float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -29,9 +31,14 @@ class RMSNorm(Norm):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name]
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def params(self) -> Optional[NormParams]:
         return NormParams(self.weight, self.eps, self.dim)
 
     def forward(self, hidden, delta, out, row_index=None) -> None:
         ops.add_rmsnorm(hidden, delta, self.weight, out, self.eps, row_index)
+
+    def forward_branch(self, branch, hidden, rounded=None) -> None:
+        ops.rmsnorm_add(branch, self.weight, hidden, self.eps, rounded)

@@ -19,22 +19,41 @@ def rope_inverse_frequencies(dim: int, theta: float) -> torch.Tensor:
     return 1.0 / (theta ** (idx / dim))
 
 
+def rope_inverse_frequencies_exact(dim: int, theta: float) -> torch.Tensor:
+    """theta^(-2j/dim), j = 0..dim/2-1, worked out in float64 and rounded once to float32."""
+    idx = torch.arange(0, dim, step=2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(theta), dtype=torch.float64), -idx / dim).to(torch.float32)
+
+
 @register_part("position_encoding", "rotary")
 class RotaryEncoding(PositionEncoding):
     """x'[j] = x[j] cos - x[j+r/2] sin, x'[j+r/2] = x[j+r/2] cos + x[j] sin over the first
     `dim` (= r) entries of each head, angle = position * inv_freq[j] in float32
     (engine/nn/rope.py:105-123, engine/kernels/triton/rope.py:22-65).  The rotation
-    itself runs inside the fused q/k kernel; this part owns the frequencies."""
+    itself runs inside the fused q/k kernel; this part owns the frequencies.
+
+    `pairing` "half" (the default) is the above; "neighbours" turns entry 2i with entry 2i+1 by
+    the same angles (mixers whose kernels take a pairing ask for it through `pairing`; the fused
+    q/k kernels of the attention mixer know the half pairing only, so `rotary_inv_freq()` answers
+    None for the other and that mixer falls back to `apply`, which this part does not offer).
+    `exact_frequencies`: the inverse frequencies are worked out in float64 before they are rounded."""
 
     graph_safe = True
 
-    def __init__(self, ctx: BuildContext, *, dim: int, theta: float) -> None:
+    def __init__(self, ctx: BuildContext, *, dim: int, theta: float, pairing: str = "half", exact_frequencies: bool = False) -> None:
         if dim % 2:
             raise ValueError(f"rotary width must be even, got {dim}")
-        self.dim, self.theta = int(dim), float(theta)
-        self.inv_freq = rope_inverse_frequencies(self.dim, self.theta).to(ctx.device)
+        if pairing not in ops.ROTARY_PAIRINGS:
+            raise ValueError(f"rotary pairing must be one of {sorted(ops.ROTARY_PAIRINGS)}, got {pairing!r}")
+        self.dim, self.theta, self.pairing = int(dim), float(theta), pairing
+        make = rope_inverse_frequencies_exact if exact_frequencies else rope_inverse_frequencies
+        self.inv_freq = make(self.dim, self.theta).to(ctx.device)
 
     def rotary_inv_freq(self) -> Optional[torch.Tensor]:
+        return self.inv_freq if self.pairing == "half" else None
+
+    def frequencies(self) -> torch.Tensor:
+        """[dim/2] float32 inverse frequencies, whatever the pairing (for kernels that take one)."""
         return self.inv_freq
 
     def rotary_cos_sin(self, step: StepContext) -> Optional[torch.Tensor]:

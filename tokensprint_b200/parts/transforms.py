@@ -1,0 +1,47 @@
+"""Transforms on the embedding rows that the package itself offers."""
+
+from __future__ import annotations
+
+from typing import Mapping, Optional
+
+import torch
+
+from tokensprint_b200 import ops
+from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, StepContext, TensorSpec, Transform, register_part
+
+
+@register_part("transform", "pair_hash_embedding")
+class PairHashEmbedding(Transform):
+    """Adds to every token's embedding row a row of a second table, picked by a hash of the token
+    before it and the token itself:  x[t] += table[(id[t-1] * mul_prev + id[t] * mul_cur) mod buckets];
+    the first token of a sequence takes the table's last row (index `buckets`).
+
+    The token before a step's first token of a request was part of an earlier step: one int32 word
+    per request (a state slot) keeps the last token a request has run, also when that token never
+    reached the host (ids fed on the device)."""
+
+    graph_safe = True
+    reads_through_ops = True
+
+    def __init__(self, ctx: BuildContext, *, table: str, buckets: int, mul_prev: int, mul_cur: int, hidden_size: int, vocab_size: int) -> None:
+        self.name, self.buckets, self.mul_prev, self.mul_cur = table, int(buckets), int(mul_prev), int(mul_cur)
+        self.hidden_size, self.vocab_size = int(hidden_size), int(vocab_size)
+        if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError("pair_hash_embedding: buckets must be positive and the multipliers not negative")
+        self.table: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.buckets + 1, self.hidden_size))]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.table = tensors[self.name]
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="none", state_shape=(1,), state_dtype=torch.int32)
+
+    def forward(self, x: torch.Tensor, step: Optional[StepContext], cache: Optional[LayerCache] = None) -> torch.Tensor:
+        if step is None or cache is None or cache.state is None:
+            raise ops.KernelError("pair_hash_embedding: needs the step's context and its state slots")
+        ops.pair_hash_embed(x, self.table, step.token_ids, step.positions, step.seq_index, step.cu_seqlens_q, step.state_slots,
+                            cache.state.view(-1), self.buckets, self.mul_prev, self.mul_cur, self.vocab_size)
+        return x
