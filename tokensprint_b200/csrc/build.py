@@ -236,6 +236,7 @@ def build_all() -> list[Path]:
     with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 2, 8)) as pool:
         paths += list(pool.map(lambda d: build_variant("attention_mma", {"TS_HEAD_DIM": d}), ATTENTION_HEAD_DIMS))
     paths.append(build_variant("attention_tcgen05", {"TS_HEAD_DIM": 128}))
+    paths.append(build_variant("latent_attention_mma", {"TS_LAT_RANK": 512, "TS_LAT_ROT": 64}))
     return paths
 
 

@@ -744,6 +744,97 @@ def moe_combine(pair_out: torch.Tensor, shared: Optional[torch.Tensor], out: tor
 
 
 # ---------------------------------------------------------------------------
+# tensor-core latent attention (one library per (rank, rotated width))
+
+LATENT_MMA_MAX_SPLITS = 64
+_latent_mma_libs: dict[tuple[int, int], tuple] = {}
+_sm_counts: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+def latent_attention_mma_supported(rank: int, rot_dim: int) -> bool:
+    """Sizes the tensor-core kernel is compiled for: multiples of 16, and tiles of 32 query rows and
+    2 x 64 cached rows that fit an SM's shared memory."""
+    if rank <= 0 or rank % 16 or rot_dim % 16 or rot_dim < 0:
+        return False
+    row = (rank + rot_dim + 8) * 2
+    return (32 + 2 * 64) * row + 2 * 16 * 72 * 2 + 1024 <= 227 * 1024
+
+
+def _latent_mma_fns(rank: int, rot_dim: int):
+    key = (rank, rot_dim)
+    fns = _latent_mma_libs.get(key)
+    if fns is None:
+        lib = _build.load_variant("latent_attention_mma", {"TS_LAT_RANK": rank, "TS_LAT_ROT": rot_dim})
+        fn = lib.ts_latent_attention_mma
+        fn.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p]
+        fn.restype = _c_int
+        for name in ("ts_latent_attention_mma_rows", "ts_latent_attention_mma_keys"):
+            getattr(lib, name).restype = _c_int
+        fns = _latent_mma_libs[key] = (fn, lib.ts_latent_attention_mma_rows(), lib.ts_latent_attention_mma_keys())
+    return fns
+
+
+def latent_attention_splits(device: torch.device, num_seqs: int, rows_per_seq: int, plan_context: int, rank: int, rot_dim: int) -> int:
+    """Into how many key ranges a step of few rows per sequence cuts each sequence's keys, so that about
+    two CTAs per SM run: a function of the batch's size and the planned context only (a captured
+    step is replayed for every length), never more ranges than pairs of key blocks."""
+    _, rows, keys = _latent_mma_fns(rank, rot_dim)
+    ctas = max(1, num_seqs * -(-rows_per_seq // rows))
+    by_work = -(-2 * _sm_count(device) // ctas)
+    by_keys = max(1, plan_context // (2 * keys))
+    return max(1, min(by_work, by_keys, LATENT_MMA_MAX_SPLITS))
+
+
+def latent_attention_mma(q_abs: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gates: Optional[torch.Tensor],
+                         cu_seqlens: torch.Tensor, context_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, num_seqs: int,
+                         max_seqlen_q: int, num_heads: int, rank: int, rot_dim: int, scale: float, window: int = 0, splits: int = 1) -> None:
+    """Causal attention of absorbed queries over cached rows on the tensor cores (bfloat16): q_abs
+    [T, H, rank+rot] holds exactly the tokens of sequences 0..num_seqs-1 (cu_seqlens), cache [pages,
+    page, rank+rot], out [T, H, rank] = softmax(q . row * scale) @ row[:rank] * gates.  `splits` > 1
+    cuts every sequence's keys into that many ranges (steps of few rows) merged by a second kernel."""
+    flush_gemm_chain()
+    _cuda_contig("q_abs", q_abs, torch.bfloat16)
+    _cuda_contig("cache", cache, torch.bfloat16)
+    _cuda_contig("out", out, torch.bfloat16)
+    for name, t in (("cu_seqlens", cu_seqlens), ("context_lens", context_lens)):
+        _cuda_contig(name, t, torch.int32)
+    if block_table.dtype != torch.int32 or block_table.dim() != 2 or block_table.stride(1) != 1:
+        raise KernelError("latent_attention_mma: block_table must be an int32 matrix with unit inner stride")
+    T, H, D = q_abs.shape[0], num_heads, rank + rot_dim
+    if not latent_attention_mma_supported(rank, rot_dim):
+        raise KernelError(f"latent_attention_mma: rank {rank} and rotated width {rot_dim} must be multiples of 16 that fit shared memory")
+    if q_abs.numel() != T * H * D or out.numel() != T * H * rank or tuple(cache.shape[-2:]) != (page_size, D):
+        raise KernelError(f"latent_attention_mma: q_abs {tuple(q_abs.shape)}, out {tuple(out.shape)}, cache {tuple(cache.shape)} disagree")
+    if cu_seqlens.numel() < num_seqs + 1 or context_lens.numel() < num_seqs or block_table.shape[0] < num_seqs:
+        raise KernelError("latent_attention_mma: the index arrays are shorter than the batch")
+    if gates is not None:
+        _cuda_contig("gates", gates, torch.float32)
+        if gates.numel() != T * H:
+            raise KernelError("latent_attention_mma: gates must be [T, heads]")
+    if not 1 <= splits <= LATENT_MMA_MAX_SPLITS:
+        raise KernelError(f"latent_attention_mma: splits must lie in 1..{LATENT_MMA_MAX_SPLITS}")
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(splits * T * H * (rank + 2), device=q_abs.device, dtype=torch.float32)
+    fn, _, _ = _latent_mma_fns(rank, rot_dim)
+    _check("latent_attention_mma", fn(
+        q_abs.data_ptr(), cache.data_ptr(), out.data_ptr(), _ptr(gates), cu_seqlens.data_ptr(), context_lens.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), page_size, num_seqs, max_seqlen_q, T, H, float(scale), int(window), int(splits),
+        _ptr(scratch), _stream()))
+    if splits > 1:
+        global launch_count
+        launch_count += 1  # the merge kernel
+
+
+# ---------------------------------------------------------------------------
 # tensor-core attention (one library per head size)
 
 # Decode steps with 2..8 key splits: the splits of a (sequence, KV head) pair form a thread-block
@@ -1512,7 +1603,7 @@ def library_mm(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor
 _TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_store", "attention_paged_simple",
           "sample", "sgemm_nt", "attention_paged_mma", "attention_decode_flat", "attention_prefill_tcgen05", "gemm_skinny_bf16",
           "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm", "sgemm_nt_batched", "library_bmm", "pair_hash_embed",
-          "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "gelu_tanh", "capped_glu", "gelu_gate_rows",
+          "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "latent_attention_mma", "gelu_tanh", "capped_glu", "gelu_gate_rows",
           "router_topk", "moe_plan", "moe_gate_up", "moe_down", "moe_combine")
 _plain_functions: dict[str, object] = {}
 _kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []

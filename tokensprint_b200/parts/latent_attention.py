@@ -3,6 +3,7 @@ latent row and one rotated key part, shared by all heads."""
 
 from __future__ import annotations
 
+import os
 from typing import Mapping, Optional
 
 import torch
@@ -10,6 +11,12 @@ import torch
 from tokensprint_b200 import ops
 from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, Mixer, PartSpec, StepContext, TensorSpec, build_part, register_part
 from tokensprint_b200.parts.linear import linear
+
+
+# TS_LATENT_ATTENTION_MMA=0 (for measurements): bfloat16 steps also run the CUDA-core kernel.
+LATENT_ATTENTION_MMA = os.environ.get("TS_LATENT_ATTENTION_MMA", "1") != "0"
+# Up to this many tokens per sequence a step's keys are cut into ranges (decode, and the shortest portions).
+LATENT_DECODE_MAX_TOKENS = 4
 
 
 def batched_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -130,6 +137,31 @@ class LatentAttentionMixer(Mixer):
         return linear(heads_out.view(T, H * self.value_dim), self.o_weight, next_weight=step.weight_after)
 
     def _attend(self, q_abs, out, gates, step: StepContext, cache: LayerCache, tables) -> None:
-        ops.latent_attention_simple(
-            q_abs, cache.k_pages, out, gates, step.positions, step.seq_index, tables.block_table, step.page_size, self.num_heads,
-            self.kv_rank, self.rot_dim, self.scale, self.window)
+        H, R, rot = self.num_heads, self.kv_rank, self.rot_dim
+        if q_abs.dtype != torch.bfloat16 or not LATENT_ATTENTION_MMA or not ops.latent_attention_mma_supported(R, rot):
+            # float32 runs, and sizes the tensor-core kernel is not made for
+            ops.latent_attention_simple(
+                q_abs, cache.k_pages, out, gates, step.positions, step.seq_index, tables.block_table, step.page_size, H, R, rot,
+                self.scale, self.window)
+            return
+        B, singles = step.num_seqs, step.decode_seqs
+
+        def run(first: int, count: int, t0: int, t1: int, max_q: int, split: bool) -> None:
+            splits = 1
+            if split:
+                context = ops.attention_decode_plan_context(step.max_context_len, self.window)
+                splits = ops.latent_attention_splits(q_abs.device, count, max_q * H, context, R, rot)
+            ops.latent_attention_mma(
+                q_abs[t0:t1], cache.k_pages, out[t0:t1], None if gates is None else gates[t0:t1], step.cu_seqlens_q[first : first + count + 1],
+                step.context_lens[first : first + count], tables.block_table[first : first + count], step.page_size, count, max_q, H, R, rot,
+                self.scale, self.window, splits)
+
+        T = q_abs.shape[0]
+        if step.max_seqlen_q <= LATENT_DECODE_MAX_TOKENS:
+            run(0, B, 0, T, step.max_seqlen_q, True)  # few rows per sequence: the keys are spread over CTAs
+        elif 0 < singles < B:
+            # single decoded tokens beside portions of prompts (the runner put the single tokens' requests first)
+            run(0, singles, 0, singles, 1, True)
+            run(singles, B - singles, 0, T, step.max_seqlen_q, False)  # their cu_seqlens count from the step's first token
+        else:
+            run(0, B, 0, T, step.max_seqlen_q, False)
