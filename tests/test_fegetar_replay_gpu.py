@@ -19,7 +19,10 @@ from tests.replay_helpers import first_bad, replay_in_process, trace_decode_tail
 
 pytestmark = pytest.mark.gpu
 
-TOLERANCE = {"float32": 1e-4, "bfloat16": 4e-2}
+# Largest allowed |engine - plain| relative to the largest |logit| of the sequence.  bfloat16: the worst
+# position of all these runs strays 5.1e-2 (the same position in every cutting, which float32 holds to
+# 1e-4); wrong keys, pages and slots are hunted in float32 here and with made-up rows in the kernel tests.
+TOLERANCE = {"float32": 1e-4, "bfloat16": 8e-2}
 SHARP = {"float32": 3.0, "bfloat16": 1.0}
 ROUTED_SHARE = {"float32": 1.0, "bfloat16": 0.01}
 LENGTHS = {"a": [1, 5, 17, 64, 100, 131], "b": [2, 9, 33, 90, 150], "c": [3, 26, 70, 129, 190]}
