@@ -737,6 +737,9 @@ def main() -> int:
                         "(the events cost host time: take the throughput from a run without this option)")
     p.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                    help="a serving loop through generate() instead of the decode benchmark (one JSON line)")
+    p.add_argument("--designs", action="store_true",
+                   help="Fegetar beside Qwen3 dense at equal size (a few layers of realistic widths, random weights): prompt and "
+                        "decode throughput and the attention kernels against their rooflines (one JSON line)")
     p.add_argument("--probe", choices=["decode", "prefill"], default=None,
                    help="run a few steps inside cudaProfilerStart/Stop for ncu and exit (see profiles/)")
     args = p.parse_args()
@@ -747,7 +750,11 @@ def main() -> int:
         return run_probe(args)
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.designs:
+        from tokensprint_b200 import design_bench
+
+        result = design_bench.run(min(args.steps, 32), args.warmup, load_peaks())
+    elif args.impl == "reference":
         result = run_reference(args)
     else:
         result = run_workload(args) if args.workload else run_ours(args)

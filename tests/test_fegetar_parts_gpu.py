@@ -280,3 +280,52 @@ def test_router_picks_by_score_and_breaks_ties_by_index():
     assert torch.allclose(w.cpu(), torch.sigmoid(torch.tensor([[2.0, 2.0, 1.0], [5.0, 0.5, 0.25]])))
     ops.router_topk(logits, 3, True, ids, w)
     assert torch.allclose(w.sum(-1).cpu(), torch.ones(2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T, W, E, top", [(1, 72, 7, 3), (9, 256, 12, 1), (130, 1000, 33, 4)])
+def test_router_in_one_kernel(dtype, T, W, E, top):
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(T)
+    x, r = torch.randn(T, W, generator=g).to(dtype), torch.randn(E, W, generator=g) / W ** 0.5
+    ids = torch.empty((T, top), dtype=torch.int32, device="cuda")
+    w = torch.empty((T, top), dtype=torch.float32, device="cuda")
+    ops.router(_dev(x), _dev(r), top, False, ids, w)
+    score = torch.sigmoid(x.double() @ r.double().T)
+    want_w, want_e = torch.topk(score, top, dim=-1)
+    assert torch.equal(ids.cpu().long(), want_e)
+    assert torch.allclose(w.cpu().double(), want_w, atol=1e-6)
+
+
+@pytest.mark.parametrize("P, E, K, I", [(1, 3, 64, 48), (70, 5, 96, 200), (300, 4, 520, 72), (40, 9, 128, 24)])
+def test_expert_products_on_tensor_cores_against_cuda_cores(P, E, K, I, monkeypatch):
+    """The same plan through both kernels; bfloat16, float32 sums in both."""
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(P)
+    top = 2 if P % 2 == 0 else 1
+    T = P // top
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    gate, up = (torch.randn(E, I, K, generator=g) / K ** 0.5).to(torch.bfloat16).cuda(), (torch.randn(E, I, K, generator=g) / K ** 0.5).to(torch.bfloat16).cuda()
+    down = (torch.randn(E, K, I, generator=g) / I ** 0.5).to(torch.bfloat16).cuda()
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32).cuda()
+    w = (torch.rand(T * top, generator=g) * 0.8 + 0.1).cuda()
+    plan = ops.moe_plan(ids, E)
+    results = []
+    for mma in (True, False):
+        monkeypatch.setattr(ops, "MOE_MMA", mma)
+        act = torch.zeros((T * top, I), dtype=torch.bfloat16, device="cuda")
+        out = torch.zeros((T * top, K), dtype=torch.bfloat16, device="cuda")
+        ops.moe_gate_up(x, w, plan, gate, up, act, top, 1.5, 1.702)
+        ops.moe_down(act, plan, down, out)
+        results.append((act.float().cpu(), out.float().cpu()))
+    # against float64, pair by pair
+    for pair in range(T * top):
+        e, h = int(ids.view(-1)[pair]), x[pair // top].double().cpu() * float(w[pair])
+        a = (gate[e].double().cpu() @ h).clamp(max=1.5)
+        b = (up[e].double().cpu() @ h).clamp(-1.5, 1.5)
+        want = down[e].double().cpu() @ (a * torch.sigmoid(1.702 * a) * (b + 1))
+        for act, out in results:
+            assert float((out[pair].double() - want).abs().max()) < 3e-2 * float(want.abs().max()) + 1e-3
+    assert float((results[0][1] - results[1][1]).abs().max()) < 2e-2 * float(results[1][1].abs().max())

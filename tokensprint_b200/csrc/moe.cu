@@ -306,3 +306,111 @@ TS_EXPORT int ts_moe_combine(const void* pair_out, const void* shared, void* out
                      (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, pair_weight, N, top, total);
   return TS_ERR_BAD_ARGUMENT;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The router in one kernel: float32 logits of RT tokens against every expert's row, then the
+// choice.  A block keeps its tokens' rows in shared memory as float32 (they come as the float32
+// residual rows or as their rounding in the compute type) and every warp walks expert rows with
+// 16-byte loads, so a router row is read once per RT tokens.  A logit's sum runs over the width
+// in a fixed order (lane-strided partial sums, then the warp's tree): it does not depend on the
+// tokens beside it.
+#define ROUTER_MAX_TOKENS 4
+
+template <typename TX>
+__global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, const float* __restrict__ router, int T, int W, int E,
+                                                     int top, int renormalize, int rt, int* __restrict__ ids,
+                                                     float* __restrict__ weights) {
+  ts_pdl_prologue();
+  extern __shared__ float rs[];
+  float* xs = rs;                    // [rt][W]
+  float* logits = rs + (size_t)rt * W;  // [rt][E]
+  const int t0 = blockIdx.x * rt;
+  const int nt = min(rt, T - t0);
+  for (int i = threadIdx.x; i < nt * W; i += blockDim.x) xs[i] = ts_to_float(x[(size_t)t0 * W + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    const float* row = router + (size_t)e * W;
+    float acc[ROUTER_MAX_TOKENS] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = lane; k < W; k += 32) {
+      const float w = row[k];
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_TOKENS; ++j)
+        if (j < nt) acc[j] = fmaf(xs[(size_t)j * W + k], w, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < ROUTER_MAX_TOKENS; ++j) {
+      const float v = ts_warp_sum(acc[j]);
+      if (lane == 0 && j < nt) logits[(size_t)j * E + e] = v;
+    }
+  }
+  __syncthreads();
+  if (warp >= nt) return;
+  const float* z = logits + (size_t)warp * E;
+  int* my_ids = ids + (size_t)(t0 + warp) * top;
+  float* my_w = weights + (size_t)(t0 + warp) * top;
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= (my_ids[j] == e);
+      const float v = z[e];
+      if (!taken && (v > best || (v == best && e < best_e))) {
+        best = v;
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ov > best || (ov == best && oe < best_e)) {
+        best = ov;
+        best_e = oe;
+      }
+    }
+    const float score = 1.f / (1.f + expf(-best));
+    total += score;
+    if (lane == 0) {
+      my_ids[k] = best_e < E ? best_e : 0;
+      my_w[k] = score;
+    }
+    __syncwarp();
+  }
+  if (renormalize && lane == 0)
+    for (int k = 0; k < top; ++k) my_w[k] /= total;
+}
+
+TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, int T, int W, int E, int top, int renormalize, int* ids,
+                        float* weights, void* stream) {
+  if (T <= 0) return 0;
+  if (W <= 0 || E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
+  int rt = ROUTER_MAX_TOKENS;
+  while (rt > 1 && (size_t)rt * (W + E) * sizeof(float) > 200 * 1024) rt >>= 1;
+  const size_t smem = (size_t)rt * (W + E) * sizeof(float);
+  if (smem > 227 * 1024) return TS_ERR_UNSUPPORTED_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 grid((T + rt - 1) / rt);
+  if (x_dtype == TS_DTYPE_F32) {
+    static size_t set32 = 0;
+    if (smem > 48 * 1024 && smem > set32) {
+      cudaError_t e = cudaFuncSetAttribute(router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+      if (e != cudaSuccess) return (int)e;
+      set32 = 227 * 1024;
+    }
+    return ts_launch(router_kernel<float>, grid, dim3(256), smem, s, (const float*)x, router, T, W, E, top, renormalize, rt, ids, weights);
+  }
+  if (x_dtype == TS_DTYPE_BF16) {
+    static size_t set16 = 0;
+    if (smem > 48 * 1024 && smem > set16) {
+      cudaError_t e = cudaFuncSetAttribute(router_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024));
+      if (e != cudaSuccess) return (int)e;
+      set16 = 227 * 1024;
+    }
+    return ts_launch(router_kernel<__nv_bfloat16>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x, router, T, W, E, top, renormalize, rt,
+                     ids, weights);
+  }
+  return TS_ERR_BAD_ARGUMENT;
+}

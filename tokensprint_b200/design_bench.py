@@ -1,0 +1,192 @@
+"""Two designs side by side at equal size: Fegetar (latent attention, dense and routed feed-forwards)
+and Qwen3 dense (grouped-query attention, SwiGLU), random weights, a few layers of widths that
+resemble a real model's.  For each: one prompt of PREFILL_TOKENS tokens as one step, decode steps
+at two batch sizes (graphs, as generation runs them), and the device time per kernel class of an
+eager prompt step and an eager decode step, with the attention kernels' distance from their
+rooflines (prompt: flops against the measured bf16 peak; decode: cache bytes against the measured
+copy bandwidth).  `python bench.py --designs` prints one JSON line.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+PREFILL_TOKENS = 2048
+DECODE_CONTEXT = 1024
+DECODE_BATCHES = (8, 64)
+PAGE = 16
+VOCAB = 32768
+
+# name -> (width, heads, layers); the latent is 512 + 64 wide and a head 128 (+ 64 rotated) as in
+# published models of this kind; half of the layers are dense, half routed
+SIZES = {
+    "w2048": dict(width=2048, heads=16, layers=4, dense_ff=8192, experts=16, top=2, expert_ff=1024, shared_ff=2048),
+    "w4096": dict(width=4096, heads=32, layers=4, dense_ff=12288, experts=32, top=4, expert_ff=1536, shared_ff=3072),
+}
+
+
+def fegetar_config(s: dict) -> dict:
+    mixer = {"heads": s["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+             "rot": {"base": 1000000.0, "dims": 64}}
+    dense = {"kind": "dense", "ff": s["dense_ff"]}
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"], "limit": 7.0},
+           "shared": {"ff": s["shared_ff"], "limit": 7.0}}
+    return {"architecture": "Fegetar", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "token_side": {"dim": 64},
+            "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(s["layers"])]}
+
+
+def fegetar_ff_params(s: dict) -> float:
+    """Feed-forward weights a token reads per layer, averaged over the dense and the routed layers."""
+    W = s["width"]
+    return (2 * W * s["dense_ff"] + 3 * W * (s["top"] * s["expert_ff"] + s["shared_ff"])) / 2
+
+
+def qwen3_config(s: dict) -> dict:
+    W = s["width"]
+    inter = int(round(fegetar_ff_params(s) / (3 * W) / 64)) * 64  # SwiGLU of the same weight per token
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": s["layers"], "hidden_size": W,
+            "num_attention_heads": s["heads"], "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": inter, "vocab_size": VOCAB,
+            "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+            "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
+
+
+def _random_ids(n: int, seed: int) -> list[int]:
+    import torch
+
+    return torch.randint(0, VOCAB, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def _measure(model, steps: int, warmup: int) -> dict[str, Any]:
+    import torch
+
+    from tokensprint_b200 import ops
+    from tokensprint_b200.engine.runner import ModelRunner, StepEntry
+
+    out: dict[str, Any] = {}
+    pages = max(DECODE_BATCHES) * (-(-(DECODE_CONTEXT + warmup + steps + 8) // PAGE)) + PREFILL_TOKENS // PAGE + 16
+    runner = ModelRunner(model, page_size=PAGE, num_pages=pages, num_slots=max(DECODE_BATCHES), max_num_batched_tokens=8192,
+                         enforce_eager=False, max_model_len=DECODE_CONTEXT + warmup + steps + 64)
+    cm = runner.cache_manager
+
+    def prefill_once(seed: int) -> float:
+        rc = cm.admit(("prefill", seed))
+        cm.extend(rc, 0, PREFILL_TOKENS)
+        entry = StepEntry(rc, _random_ids(PREFILL_TOKENS, seed), 0, [PREFILL_TOKENS - 1])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        runner.step([entry])
+        b.record()
+        torch.cuda.synchronize()
+        runner.free(rc)
+        return a.elapsed_time(b)
+
+    times = sorted(prefill_once(r) for r in range(7))[1:-1]
+    out["prefill_ms"] = round(times[len(times) // 2], 3)
+    out["prefill_tokens_per_s"] = round(PREFILL_TOKENS / out["prefill_ms"] * 1e3)
+    ops.time_kernels(True)
+    ops.kernel_times()
+    prefill_once(99)
+    out["prefill_kernels"] = ops.kernel_times()
+    ops.time_kernels(False)
+
+    for batch in DECODE_BATCHES:
+        reqs = [cm.admit(("decode", batch, b)) for b in range(batch)]
+        for i in range(0, batch, 8):
+            entries = []
+            for b in range(i, min(batch, i + 8)):
+                cm.extend(reqs[b], 0, DECODE_CONTEXT)
+                entries.append(StepEntry(reqs[b], _random_ids(DECODE_CONTEXT, 100 + b), 0, []))
+            runner.step(entries)
+        tokens = [_random_ids(warmup + steps + 1, 500 + b) for b in range(batch)]
+
+        def one(i: int) -> None:
+            pos = DECODE_CONTEXT + i
+            entries = []
+            for b in range(batch):
+                cm.extend(reqs[b], pos, pos + 1)
+                entries.append(StepEntry(reqs[b], [tokens[b][i]], pos, [0]))
+            runner.step(entries)
+
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        b_.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b_) / steps
+        out[f"decode_b{batch}_ms"] = round(ms, 4)
+        out[f"decode_b{batch}_tokens_per_s"] = round(batch / ms * 1e3)
+        # one more step launched kernel by kernel, with a timer around every class
+        graphs, runner.use_graphs = runner.use_graphs, False
+        ops.time_kernels(True)
+        ops.kernel_times()
+        one(warmup + steps)
+        out[f"decode_b{batch}_kernels"] = ops.kernel_times()
+        ops.time_kernels(False)
+        runner.use_graphs = graphs
+        for rc in reqs:
+            runner.free(rc)
+    out["graphs"] = bool(runner._graphs)
+    return out
+
+
+def _attention_rooflines(design: str, s: dict, m: dict, peaks: dict) -> dict[str, Any]:
+    """Achieved / roofline of the attention kernels from the per-class timers (all layers summed)."""
+    L, H, T = s["layers"], s["heads"], PREFILL_TOKENS
+    pairs = T * (T + 1) / 2
+    if design == "fegetar":
+        names = ("latent_attention_mma",)
+        flops = L * 2 * H * pairs * (576 + 512)
+        row_bytes = 576 * 2
+    else:
+        names = ("attention_prefill_tcgen05", "attention_paged_mma", "attention_decode_flat")
+        flops = L * 4 * H * 128 * pairs
+        row_bytes = 2 * 8 * 128 * 2
+    out: dict[str, Any] = {}
+
+    def ms_of(kernels: dict) -> float:
+        return sum(v["ms"] for k, v in kernels.items() if k in names)
+
+    ms = ms_of(m["prefill_kernels"])
+    if ms > 0:
+        out["prefill_attention_ms"] = round(ms, 3)
+        out["prefill_attention_of_bf16_peak"] = round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 3)
+    for batch in DECODE_BATCHES:
+        ms = ms_of(m[f"decode_b{batch}_kernels"])
+        if ms > 0:
+            out[f"decode_b{batch}_attention_ms"] = round(ms, 4)
+            out[f"decode_b{batch}_attention_of_hbm_peak"] = round(L * batch * DECODE_CONTEXT * row_bytes / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)
+    return out
+
+
+def run(steps: int, warmup: int, peaks: dict) -> dict[str, Any]:
+    import gc
+
+    import torch
+
+    from tokensprint_b200.config.registry import architecture_for
+    from tokensprint_b200.models.api import random_model
+
+    result: dict[str, Any] = {"metric": "design_comparison", "dtype": "bf16", "data": "synthetic, random weights",
+                              "prefill_tokens": PREFILL_TOKENS, "decode_context": DECODE_CONTEXT, "sizes": {}}
+    for name, s in SIZES.items():
+        row: dict[str, Any] = {"size": s}
+        for design, cfg_dict in (("fegetar", fegetar_config(s)), ("qwen3", qwen3_config(s))):
+            cfg = architecture_for(cfg_dict).config_from_dict(cfg_dict)
+            model = random_model(cfg, seed=1, device="cuda", dtype="bfloat16", generate_on_device=True)
+            m = _measure(model, steps, warmup)
+            m["weight_bytes"] = model.weight_bytes()
+            m.update(_attention_rooflines(design, s, m, peaks))
+            row[design] = m
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        result["sizes"][name] = row
+    return result
+
+

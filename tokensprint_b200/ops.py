@@ -52,6 +52,10 @@ _SIGNATURES = {
     "ts_capped_glu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "ts_gelu_gate_rows": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_void_p],
     "ts_router_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "ts_router": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "ts_moe_gate_up_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_float, _c_float, _c_void_p],
+    "ts_moe_down_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_moe_plan": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "ts_moe_gate_up": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_float, _c_float, _c_void_p],
@@ -669,6 +673,26 @@ def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Te
     _check("router_topk", _fn("ts_router_topk")(logits.data_ptr(), T, E, int(top), int(bool(renormalize)), ids.data_ptr(), weights.data_ptr(), _stream()))
 
 
+def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Logits and choice in one kernel: rows [T, W] (float32, or bfloat16 widened on the fly) against
+    router_weight [E, W] float32 with float32 sums, then as router_topk."""
+    flush_gemm_chain()
+    _cuda_contig("rows", rows)
+    _cuda_contig("router_weight", router_weight, torch.float32)
+    _cuda_contig("ids", ids, torch.int32)
+    _cuda_contig("weights", weights, torch.float32)
+    T, W = rows.shape
+    E = router_weight.shape[0]
+    if router_weight.shape[1] != W or not 0 < top <= E or ids.numel() != T * top or weights.numel() != T * top:
+        raise KernelError(f"router: rows {tuple(rows.shape)}, router {tuple(router_weight.shape)}, top {top}, ids {tuple(ids.shape)}")
+    _check("router", _fn("ts_router")(rows.data_ptr(), _act_code("rows", rows), router_weight.data_ptr(), T, W, E, int(top),
+                                      int(bool(renormalize)), ids.data_ptr(), weights.data_ptr(), _stream()))
+
+
+# TS_MOE_MMA=0 (for measurements): bfloat16 expert products on CUDA cores too.
+MOE_MMA = _os.environ.get("TS_MOE_MMA", "1") != "0"
+
+
 def moe_plan(ids: torch.Tensor, num_experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Sorts the (token, choice) pairs of ids [T, top] by expert on the device.  Returns offsets
     [E+1] (expert e's places are offsets[e]..offsets[e+1]), tile_offsets [E+1] (its first row tile of
@@ -700,6 +724,11 @@ def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple[torch.Te
     P = T * top
     if K2 != K or up.shape != gate.shape or act.shape != (P, I) or pair_weight.numel() != P or order.numel() != P:
         raise KernelError(f"moe_gate_up: shapes disagree: x {tuple(x.shape)}, gate {tuple(gate.shape)}, up {tuple(up.shape)}, act {tuple(act.shape)}")
+    if MOE_MMA and x.dtype == torch.bfloat16 and K % 8 == 0:
+        _check("moe_gate_up", _fn("ts_moe_gate_up_mma")(
+            x.data_ptr(), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), gate.data_ptr(),
+            up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), _stream()))
+        return
     _check("moe_gate_up", _fn("ts_moe_gate_up")(
         x.data_ptr(), _act_code("x", x), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(),
         gate.data_ptr(), up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), _stream()))
@@ -716,6 +745,11 @@ def moe_down(act: torch.Tensor, plan: tuple[torch.Tensor, torch.Tensor, torch.Te
     E, N, I2 = down.shape
     if I2 != I or pair_out.shape != (P, N) or order.numel() != P:
         raise KernelError(f"moe_down: shapes disagree: act {tuple(act.shape)}, down {tuple(down.shape)}, pair_out {tuple(pair_out.shape)}")
+    if MOE_MMA and act.dtype == torch.bfloat16 and I % 8 == 0:
+        _check("moe_down", _fn("ts_moe_down_mma")(
+            act.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), down.data_ptr(), pair_out.data_ptr(), P, E, I, N,
+            _stream()))
+        return
     _check("moe_down", _fn("ts_moe_down")(
         act.data_ptr(), _act_code("act", act), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), down.data_ptr(),
         pair_out.data_ptr(), P, E, I, N, _stream()))
@@ -1604,7 +1638,7 @@ _TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu"
           "sample", "sgemm_nt", "attention_paged_mma", "attention_decode_flat", "attention_prefill_tcgen05", "gemm_skinny_bf16",
           "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm", "sgemm_nt_batched", "library_bmm", "pair_hash_embed",
           "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "latent_attention_mma", "gelu_tanh", "capped_glu", "gelu_gate_rows",
-          "router_topk", "moe_plan", "moe_gate_up", "moe_down", "moe_combine")
+          "router_topk", "router", "moe_plan", "moe_gate_up", "moe_down", "moe_combine")
 _plain_functions: dict[str, object] = {}
 _kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
 

@@ -142,18 +142,10 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, top, dev = x.shape[0], self.top, x.device
-        if x.dtype == torch.float32:
-            rows = x
-        elif residual is not None:
-            rows = residual
-        else:
-            rows = torch.empty(x.shape, device=dev, dtype=torch.float32)
-            ops.round_rows(x, rows)
-        logits = torch.empty((T, self.num_experts), device=dev, dtype=torch.float32)
-        ops.sgemm_nt(rows, self.router, logits)
+        rows = residual if residual is not None else x  # float32 rows where the block has them, else their rounding
         chosen = torch.empty((T, top), device=dev, dtype=torch.int32)
         weights = torch.empty((T, top), device=dev, dtype=torch.float32)
-        ops.router_topk(logits, top, self.renormalize, chosen, weights)
+        ops.router(rows, self.router, top, self.renormalize, chosen, weights)
         plan = ops.moe_plan(chosen, self.num_experts)
         act = torch.empty((T * top, self.intermediate_size), device=dev, dtype=x.dtype)
         on_input = self.weight_on == "input"
