@@ -1,7 +1,7 @@
 """Times the engine's kernels one at a time, at the layer sizes of a named preset and over a
 range of batch sizes and context lengths, and prints each one's share of its roofline.
 
-    python -m tokensprint_b200.kernel_bench [--preset qwen3-8b] [--only decode,prompt,gemm,small,layer]
+    python -m tokensprint_b200.kernel_bench [--preset qwen3-8b] [--only decode,prompt,gemm,small,layer,latent,experts]
 
 Every kernel runs after a read of a buffer larger than the L2 cache, so it reads its operands
 from device memory as it does inside a model step, and is timed on the device inside a CUDA graph,
@@ -281,7 +281,77 @@ def layer_products(cfg, timer, pk, rows, device):
     ops.check_device_errors()
 
 
-GROUPS = {"decode": decode_attention, "prompt": prompt_attention, "gemm": skinny_gemm, "small": small_kernels, "layer": layer_products}
+# Latent attention and routed experts have no preset of their own here: the sizes are those of
+# published models of that kind (a latent of 512 + 64 rotated entries; experts of a few thousand rows).
+LATENT = {"rank": 512, "rot": 64, "heads": (16, 128), "page": 16}
+EXPERTS = {"width": 4096, "ff": 1536, "experts": 32, "top": 4}
+CASE_FILTER = ""  # --case: only the latent-attention cases whose "H=.. B=.. T=.. ctx=.." line contains this (a capture of one case)
+
+
+def latent_attention(cfg, timer, pk, rows, device):
+    """The tensor-core latent attention kernel: decode steps (cache bytes against the copy bandwidth)
+    and prompt portions (flops of both products against the bf16 peak)."""
+    R, rot, page = LATENT["rank"], LATENT["rot"], LATENT["page"]
+    D = R + rot
+    for H in LATENT["heads"]:
+        for B, T, ctx in ((8, 1, 1024), (64, 1, 1024), (8, 1, 16384), (64, 1, 4096), (1, 2048, 2048), (4, 2048, 2048), (1, 8192, 8192)):
+            if T > 1 and B * T * H * D * 2 > (2 << 30):
+                continue
+            if CASE_FILTER and CASE_FILTER not in f"H={H} B={B} T={T} ctx={ctx}":
+                continue
+            blocks = -(-ctx // page)
+            cache = torch.randn(B * blocks, page, D, device=device).bfloat16()
+            table = torch.randperm(B * blocks, device=device).int().view(B, blocks).contiguous()
+            q = torch.randn(B * T, H, D, device=device).bfloat16()
+            out = torch.empty(B * T, H, R, device=device, dtype=torch.bfloat16)
+            gates = torch.rand(B * T, H, device=device)
+            cu = torch.arange(0, B * T + 1, T, dtype=torch.int32, device=device)
+            lens = torch.full((B,), ctx, dtype=torch.int32, device=device)
+            splits = ops.latent_attention_splits(device, B, T * H, min(ctx, 2048), R, rot) if T <= 4 else 1
+
+            def run():
+                ops.latent_attention_mma(q, cache, out, gates, cu, lens, table, page, B, T, H, R, rot, D ** -0.5, 0, splits)
+
+            us = timer(run)
+            if T == 1:
+                gb = B * ctx * D * 2 / 1e9
+                rows.append(("latent attention, decode", f"H={H} B={B} ctx={ctx} splits={splits}", us, gb / (us * 1e-6), "GB/s", gb / (us * 1e-6) / pk["hbm_gbs"]))
+            else:
+                pairs = B * (T * (ctx - T) + T * (T + 1) / 2)
+                tf = 2 * pairs * H * (D + R) / 1e12
+                rows.append(("latent attention, prompt", f"H={H} B={B} new={T} keys={ctx}", us, tf / (us * 1e-6), "TFLOP/s", tf / (us * 1e-6) / pk["bf16_tflops"]))
+            del cache, q, out
+
+
+def routed_experts(cfg, timer, pk, rows, device):
+    """The two expert products over a plan: few tokens (the chosen experts' weights against the copy
+    bandwidth) and many (flops against the bf16 peak)."""
+    W, I, E, top = EXPERTS["width"], EXPERTS["ff"], EXPERTS["experts"], EXPERTS["top"]
+    gate = (torch.randn(E, I, W, device=device) * 0.02).bfloat16()
+    up = (torch.randn(E, I, W, device=device) * 0.02).bfloat16()
+    down = (torch.randn(E, W, I, device=device) * 0.02).bfloat16()
+    for T in (8, 64, 2048, 8192):
+        x = torch.randn(T, W, device=device).bfloat16()
+        ids = torch.stack([torch.randperm(E, device=device)[:top] for _ in range(T)]).int().contiguous()
+        w = torch.rand(T * top, device=device)
+        plan = ops.moe_plan(ids, E)
+        act = torch.empty(T * top, I, device=device, dtype=torch.bfloat16)
+        pair_out = torch.empty(T * top, W, device=device, dtype=torch.bfloat16)
+        used = int(torch.unique(ids).numel())
+        for name, fn, flops, weight_bytes in (
+                ("expert gate/up product", lambda: ops.moe_gate_up(x, w, plan, gate, up, act, top, 7.0, 1.702), 4 * T * top * I * W, used * 2 * I * W * 2),
+                ("expert down product", lambda: ops.moe_down(act, plan, down, pair_out), 2 * T * top * I * W, used * I * W * 2)):
+            us = timer(fn)
+            if T <= 64:
+                gb = weight_bytes / 1e9
+                rows.append((name, f"T={T} top={top} of {E}, {used} experts used", us, gb / (us * 1e-6), "GB/s", gb / (us * 1e-6) / pk["hbm_gbs"]))
+            else:
+                tf = flops / 1e12
+                rows.append((name, f"T={T} top={top} of {E}", us, tf / (us * 1e-6), "TFLOP/s", tf / (us * 1e-6) / pk["bf16_tflops"]))
+
+
+GROUPS = {"decode": decode_attention, "prompt": prompt_attention, "gemm": skinny_gemm, "small": small_kernels, "layer": layer_products,
+          "latent": latent_attention, "experts": routed_experts}
 
 
 def main(argv=None) -> int:
@@ -292,7 +362,10 @@ def main(argv=None) -> int:
     p.add_argument("--batches", default="1,8,64", help="batch sizes of the decode attention cases")
     p.add_argument("--contexts", default="1024,4096,16384,32768", help="context lengths of the decode attention cases")
     p.add_argument("--json", action="store_true", help="one JSON object a row instead of the table")
+    p.add_argument("--case", default="", help='group "latent": only the cases whose line "H=.. B=.. T=.. ctx=.." contains this')
     args = p.parse_args(argv)
+    global CASE_FILTER
+    CASE_FILTER = args.case
     if not torch.cuda.is_available():
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 2

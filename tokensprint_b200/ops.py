@@ -819,11 +819,11 @@ def _latent_mma_fns(rank: int, rot_dim: int):
 def latent_attention_splits(device: torch.device, num_seqs: int, rows_per_seq: int, plan_context: int, rank: int, rot_dim: int) -> int:
     """Into how many key ranges a step of few rows per sequence cuts each sequence's keys, so that about
     two CTAs per SM run: a function of the batch's size and the planned context only (a captured
-    step is replayed for every length), never more ranges than pairs of key blocks."""
+    step is replayed for every length), never more ranges than key blocks."""
     _, rows, keys = _latent_mma_fns(rank, rot_dim)
     ctas = max(1, num_seqs * -(-rows_per_seq // rows))
     by_work = -(-2 * _sm_count(device) // ctas)
-    by_keys = max(1, plan_context // (2 * keys))
+    by_keys = max(1, plan_context // keys)
     return max(1, min(by_work, by_keys, LATENT_MMA_MAX_SPLITS))
 
 
