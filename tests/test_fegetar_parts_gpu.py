@@ -298,7 +298,7 @@ def test_router_in_one_kernel(dtype, T, W, E, top):
     assert torch.allclose(w.cpu().double(), want_w, atol=1e-6)
 
 
-@pytest.mark.parametrize("P, E, K, I", [(1, 3, 64, 48), (70, 5, 96, 200), (300, 4, 520, 72), (40, 9, 128, 24)])
+@pytest.mark.parametrize("P, E, K, I", [(1, 3, 64, 48), (70, 5, 96, 200), (300, 4, 520, 72), (40, 9, 128, 24), (36, 3, 72, 136)])
 def test_expert_products_on_tensor_cores_against_cuda_cores(P, E, K, I, monkeypatch):
     """The same plan through both kernels; bfloat16, float32 sums in both."""
     from tokensprint_b200 import ops
@@ -311,10 +311,10 @@ def test_expert_products_on_tensor_cores_against_cuda_cores(P, E, K, I, monkeypa
     down = (torch.randn(E, K, I, generator=g) / I ** 0.5).to(torch.bfloat16).cuda()
     ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32).cuda()
     w = (torch.rand(T * top, generator=g) * 0.8 + 0.1).cuda()
-    plan = ops.moe_plan(ids, E)
     results = []
     for mma in (True, False):
         monkeypatch.setattr(ops, "MOE_MMA", mma)
+        plan = ops.moe_plan(ids, E, ops.moe_row_tile(ops.moe_on_tensor_cores(torch.bfloat16, K, I), T * top, E))
         act = torch.zeros((T * top, I), dtype=torch.bfloat16, device="cuda")
         out = torch.zeros((T * top, K), dtype=torch.bfloat16, device="cuda")
         ops.moe_gate_up(x, w, plan, gate, up, act, top, 1.5, 1.702)

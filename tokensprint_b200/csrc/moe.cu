@@ -5,7 +5,8 @@
 //                 scores (the lower index wins a tie) with their experts; the scores are handed on
 //                 as they are, or divided by their sum (`renormalize`).
 //   moe_plan    : the (token, choice) pairs sorted by expert: offsets[e] .. offsets[e+1] are expert
-//                 e's places in `order` (pair indices), tile_offsets[e] its first row tile.
+//                 e's places in `order` (pair indices), tile_offsets[e] its first row tile of
+//                 `tile_rows` places (64 for the kernels here, more for the tensor-core ones).
 //   moe_gate_up : for the pairs of each expert, rows x[token] * weight(pair) times the expert's gate
 //                 and up matrices, then a = min(g, limit), b = clamp(u, -limit, limit),
 //                 act = a * sigmoid(alpha a) * (b + 1)           -> act[place, I]
@@ -72,8 +73,8 @@ TS_EXPORT int ts_router_topk(const float* logits, int T, int E, int top, int ren
 }
 
 // One block: counts per expert, their prefix sums, then every pair takes the next place of its expert.
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ offsets, int* __restrict__ tile_offsets,
-                                int* __restrict__ order) {
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int P, int E, int tile_rows, int* __restrict__ offsets,
+                                int* __restrict__ tile_offsets, int* __restrict__ order) {
   ts_pdl_prologue();
   extern __shared__ int sm[];
   int* count = sm;           // [E]
@@ -92,7 +93,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int P, int E, int* 
       tile_offsets[e] = tiles;
       cursor[e] = rows;
       rows += count[e];
-      tiles += (count[e] + MOE_BM - 1) / MOE_BM;
+      tiles += (count[e] + tile_rows - 1) / tile_rows;
     }
     offsets[E] = rows;
     tile_offsets[E] = tiles;
@@ -104,10 +105,12 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int P, int E, int* 
   }
 }
 
-TS_EXPORT int ts_moe_plan(const int* ids, int P, int E, int* offsets, int* tile_offsets, int* order, void* stream) {
+TS_EXPORT int ts_moe_plan(const int* ids, int P, int E, int tile_rows, int* offsets, int* tile_offsets, int* order, void* stream) {
   if (P <= 0) return 0;
+  if (tile_rows <= 0) return TS_ERR_BAD_ARGUMENT;
   if (E <= 0 || E > MOE_MAX_EXPERTS) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, ids, P, E, offsets, tile_offsets, order);
+  return ts_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), (cudaStream_t)stream, ids, P, E, tile_rows, offsets,
+                   tile_offsets, order);
 }
 
 // Which expert a row tile belongs to: the last e with tile_offsets[e] <= tile.

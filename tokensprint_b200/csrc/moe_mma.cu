@@ -1,8 +1,8 @@
 // The two products of a routed feed-forward on the tensor cores (bfloat16, mma.sync m16n8k16,
 // float32 sums), over the plan that moe.cu makes: the (token, choice) pairs sorted by expert, in
-// row tiles of 64 places that never straddle two experts.
+// row tiles (of 128 places, or of 16 in steps of few tokens) that never straddle two experts.
 //
-// A CTA (4 warps) takes one row tile and 128 weight rows: for the first product the gate rows and
+// A CTA takes one row tile and 128 weight rows: for the first product the gate rows and
 // the up rows of the same 64 outputs (so the activation is the epilogue), for the second 128 rows
 // of the down matrix.  Both operands stream through shared memory in slices of 64 along k, three
 // slices in flight (16-byte cp.async); a row of A is the token's row (first product: found through
@@ -13,9 +13,7 @@
 
 namespace {
 
-constexpr int BM = 64, NB = 128, BK = 64, STAGES = 3, KS = BK + 8, THREADS = 128;
-constexpr size_t STAGE_ELEMS = (size_t)(BM + NB) * KS;
-constexpr size_t SMEM_BYTES = STAGES * STAGE_ELEMS * 2;
+constexpr int NB = 128, BK = 64, KS = BK + 8;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -41,13 +39,17 @@ __device__ __forceinline__ int tile_expert(const int* __restrict__ tile_offsets,
   return lo;
 }
 
-// GATE_UP: B rows 0..63 are gate rows n0.., rows 64..127 the up rows of the same outputs; else 128 rows of one matrix.
-template <bool GATE_UP>
-__global__ void __launch_bounds__(THREADS) moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const float* __restrict__ pair_weight,
-                                                          const int* __restrict__ order, const int* __restrict__ offsets,
-                                                          const int* __restrict__ tile_offsets, const __nv_bfloat16* __restrict__ B0,
-                                                          const __nv_bfloat16* __restrict__ B1, __nv_bfloat16* __restrict__ out, int E,
-                                                          int K, int NOUT, int top, float limit, float alpha) {
+// WM x WN warps: a warp owns 16 rows and NB / WN of the 128 weight rows in shared memory.  GATE_UP: the
+// first half of a warp's weight rows are gate rows and the second half the up rows of the same
+// outputs (so both operands of an activation sit in one thread); else 128 rows of one matrix.
+template <bool GATE_UP, int WM, int WN, int STAGES>
+__global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const float* __restrict__ pair_weight,
+                                                               const int* __restrict__ order, const int* __restrict__ offsets,
+                                                               const int* __restrict__ tile_offsets, const __nv_bfloat16* __restrict__ B0,
+                                                               const __nv_bfloat16* __restrict__ B1, __nv_bfloat16* __restrict__ out, int E,
+                                                               int K, int NOUT, int top, float limit, float alpha) {
+  constexpr int BM = 16 * WM, THREADS = 32 * WM * WN, CW = NB / WN, HALF = CW / 2, NT = CW / 8;
+  constexpr size_t STAGE_ELEMS = (size_t)(BM + NB) * KS;
   ts_pdl_prologue();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -84,8 +86,9 @@ __global__ void __launch_bounds__(THREADS) moe_mma_kernel(const __nv_bfloat16* _
       const __nv_bfloat16* src;
       int n;
       if (GATE_UP) {
-        n = n0 + (r & 63);
-        src = (r < 64 ? W0 : W1) + (size_t)n * K;
+        const int within = r % CW;
+        n = n0 + (r / CW) * HALF + within % HALF;
+        src = (within < HALF ? W0 : W1) + (size_t)n * K;
       } else {
         n = n0 + r;
         src = W0 + (size_t)n * K;
@@ -101,9 +104,10 @@ __global__ void __launch_bounds__(THREADS) moe_mma_kernel(const __nv_bfloat16* _
     cp_async_commit();
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, qi = lane & 3;
-  float acc[NB / 8][4];
+  const int wm = warp / WN, wn = warp % WN;
+  float acc[NT][4];
 #pragma unroll
-  for (int i = 0; i < NB / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   for (int kt = 0; kt < nk; ++kt) {
     cp_async_wait<STAGES - 2>();
@@ -111,13 +115,13 @@ __global__ void __launch_bounds__(THREADS) moe_mma_kernel(const __nv_bfloat16* _
     if (kt + STAGES - 1 < nk) load_stage(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
     const __nv_bfloat16* As = smem + (size_t)(kt % STAGES) * STAGE_ELEMS;
-    const __nv_bfloat16* Bs = As + (size_t)BM * KS;
+    const __nv_bfloat16* Bs = As + (size_t)BM * KS + (size_t)wn * CW * KS;
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
       unsigned a[4];
-      ldmatrix_x4(a, As + (size_t)(warp * 16 + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8);
+      ldmatrix_x4(a, As + (size_t)(wm * 16 + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-      for (int nb = 0; nb < NB / 16; ++nb) {
+      for (int nb = 0; nb < NT / 2; ++nb) {
         unsigned b[4];
         ldmatrix_x4(b, Bs + (size_t)(nb * 16 + (lane >> 4) * 8 + (lane & 7)) * KS + ks * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16(acc[2 * nb], a, b[0], b[1]);
@@ -129,69 +133,85 @@ __global__ void __launch_bounds__(THREADS) moe_mma_kernel(const __nv_bfloat16* _
 
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int rl = warp * 16 + quad + 8 * r;
+    const int rl = wm * 16 + quad + 8 * r;
     const int pair = a_pair[rl];
     if (pair < 0) continue;
     if (GATE_UP) {
       const float w = pair_weight[pair];
       __nv_bfloat16* dst = out + (size_t)(row0 + rl) * NOUT;
 #pragma unroll
-      for (int nb = 0; nb < 8; ++nb)
+      for (int nb = 0; nb < NT / 2; ++nb)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const int n = n0 + nb * 8 + 2 * qi + c;
+          const int n = n0 + wn * HALF + nb * 8 + 2 * qi + c;
           if (n >= NOUT) continue;
           // the sums are rounded to bfloat16 first, as a product stored to memory would be
           const float gv = __bfloat162float(__float2bfloat16_rn(w * acc[nb][2 * r + c]));
-          const float uv = __bfloat162float(__float2bfloat16_rn(w * acc[nb + 8][2 * r + c]));
+          const float uv = __bfloat162float(__float2bfloat16_rn(w * acc[nb + NT / 2][2 * r + c]));
           const float a = fminf(gv, limit), b = fminf(fmaxf(uv, -limit), limit);
           dst[n] = __float2bfloat16_rn(a / (1.f + expf(-alpha * a)) * (b + 1.f));
         }
     } else {
       __nv_bfloat16* dst = out + (size_t)pair * NOUT;
 #pragma unroll
-      for (int nb = 0; nb < NB / 8; ++nb)
+      for (int nb = 0; nb < NT; ++nb)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const int n = n0 + nb * 8 + 2 * qi + c;
+          const int n = n0 + wn * CW + nb * 8 + 2 * qi + c;
           if (n < NOUT) dst[n] = __float2bfloat16_rn(acc[nb][2 * r + c]);
         }
     }
   }
 }
 
-template <bool GATE_UP>
+// Two shapes: many rows per expert (tiles of 128 rows, 8 warps one above the other, 3 slices in
+// flight) and few (tiles of 16 rows, 4 warps side by side over the 128 weight rows, 3 slices in
+// flight, three CTAs per SM: the step then streams the chosen experts' weights and little else).
+constexpr int ROWS_MANY = 128, ROWS_FEW = 16;
+
+template <bool GATE_UP, int WM, int WN, int STAGES>
 int launch(const void* A, const float* pair_weight, const int* order, const int* offsets, const int* tile_offsets, const void* B0,
            const void* B1, void* out, int P, int E, int K, int NOUT, int top, float limit, float alpha, cudaStream_t s) {
+  constexpr int BM = 16 * WM;
+  constexpr size_t SMEM_BYTES = (size_t)STAGES * (BM + NB) * KS * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(moe_mma_kernel<GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(moe_mma_kernel<GATE_UP, WM, WN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int cols = GATE_UP ? NB / 2 : NB;
   const dim3 grid((NOUT + cols - 1) / cols, (P + BM - 1) / BM + E);
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(moe_mma_kernel<GATE_UP>, grid, dim3(THREADS), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight, order, offsets,
-                   tile_offsets, (const __nv_bfloat16*)B0, (const __nv_bfloat16*)B1, (__nv_bfloat16*)out, E, K, NOUT, top, limit, alpha);
+  return ts_launch(moe_mma_kernel<GATE_UP, WM, WN, STAGES>, grid, dim3(32 * WM * WN), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight,
+                   order, offsets, tile_offsets, (const __nv_bfloat16*)B0, (const __nv_bfloat16*)B1, (__nv_bfloat16*)out, E, K, NOUT, top,
+                   limit, alpha);
 }
 
 }  // namespace
 
-// bfloat16 only; K (the inner width) must be a multiple of 8 and every base address 16-byte aligned.
+// Places per row tile of the two shapes: what the plan's tile_offsets must be made for.
+TS_EXPORT int ts_moe_mma_row_tile(int few_rows) { return few_rows ? ROWS_FEW : ROWS_MANY; }
+
+// bfloat16 only; K (the inner width) must be a multiple of 8 and every base address 16-byte aligned;
+// tile_rows: the row tile the plan was made for (one of the two above).
 TS_EXPORT int ts_moe_gate_up_mma(const void* x, const float* pair_weight, const int* order, const int* offsets, const int* tile_offsets,
                                  const void* gate, const void* up, void* act, int P, int E, int K, int I, int top, float limit, float alpha,
-                                 void* stream) {
+                                 int tile_rows, void* stream) {
   if (P <= 0) return 0;
-  if (E <= 0 || K <= 0 || I <= 0 || top <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (E <= 0 || K <= 0 || I <= 0 || top <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (K % 8 || (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)up) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
-  return launch<true>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
+  if (tile_rows == ROWS_MANY)
+    return launch<true, 8, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
+  return launch<true, 1, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
 }
 
 TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offsets, const int* tile_offsets, const void* down,
-                              void* pair_out, int P, int E, int I, int N, void* stream) {
+                              void* pair_out, int P, int E, int I, int N, int tile_rows, void* stream) {
   if (P <= 0) return 0;
-  if (E <= 0 || I <= 0 || N <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (E <= 0 || I <= 0 || N <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (I % 8 || (((uintptr_t)act | (uintptr_t)down) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
-  return launch<false>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
+  if (tile_rows == ROWS_MANY)
+    return launch<false, 8, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
+  return launch<false, 1, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
 }

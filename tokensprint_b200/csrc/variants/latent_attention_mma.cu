@@ -74,8 +74,10 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
 
   const int b = blockIdx.y, split = blockIdx.z;
   const int q0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - q0;
-  const int rows_b = qlen * H, r0 = blockIdx.x * BM;
-  if (r0 >= rows_b) return;
+  const int rows_b = qlen * H;
+  // the last row tiles of a sequence see the most keys: they are launched first
+  const int r0 = ((rows_b + BM - 1) / BM - 1 - (int)blockIdx.x) * BM;
+  if (r0 < 0) return;
   const int pos0 = context_lens[b] - qlen;  // position of the sequence's first token of this step
   const int t_lo = r0 / H, t_hi = (min(rows_b, r0 + BM) - 1) / H;
   const int k_hi = pos0 + t_hi;
@@ -155,16 +157,29 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
     __syncthreads();
     const __nv_bfloat16* Kb = Ks + (size_t)buf * BN * DS;
 
-    // S: this warp's 16 rows against its 16 keys
-    float s[2][4] = {};
-#pragma unroll 4
-    for (int ks = 0; ks < D / 16; ++ks) {
+    // S: this warp's 16 rows against its 16 keys.  Even and odd k-steps add into sums of their own, so
+    // that four chains of dependent MMAs are in flight instead of two (a warp waits for an MMA's
+    // result many cycles, and few warps are resident to fill them).
+    float s[2][4] = {}, s_odd[2][4] = {};
+#pragma unroll 2
+    for (int ks = 0; ks < D / 16; ks += 2) {
       unsigned a[4], kf[4];
       ldmatrix_x4(a, Qs + (size_t)(rg * 16 + (lane & 15)) * DS + ks * 16 + (lane >> 4) * 8);
       ldmatrix_x4(kf, Kb + (size_t)(vq * 16 + (lane >> 4) * 8 + (lane & 7)) * DS + ks * 16 + ((lane >> 3) & 1) * 8);
       mma_bf16(s[0], a, kf[0], kf[1]);
       mma_bf16(s[1], a, kf[2], kf[3]);
+      if (ks + 1 < D / 16) {
+        unsigned a2[4], kf2[4];
+        ldmatrix_x4(a2, Qs + (size_t)(rg * 16 + (lane & 15)) * DS + (ks + 1) * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(kf2, Kb + (size_t)(vq * 16 + (lane >> 4) * 8 + (lane & 7)) * DS + (ks + 1) * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s_odd[0], a2, kf2[0], kf2[1]);
+        mma_bf16(s_odd[1], a2, kf2[2], kf2[3]);
+      }
     }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] += s_odd[nt][e];
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)

@@ -334,7 +334,7 @@ def routed_experts(cfg, timer, pk, rows, device):
         x = torch.randn(T, W, device=device).bfloat16()
         ids = torch.stack([torch.randperm(E, device=device)[:top] for _ in range(T)]).int().contiguous()
         w = torch.rand(T * top, device=device)
-        plan = ops.moe_plan(ids, E)
+        plan = ops.moe_plan(ids, E, ops.moe_row_tile(True, T * top, E))
         act = torch.empty(T * top, I, device=device, dtype=torch.bfloat16)
         pair_out = torch.empty(T * top, W, device=device, dtype=torch.bfloat16)
         used = int(torch.unique(ids).numel())

@@ -54,9 +54,9 @@ _SIGNATURES = {
     "ts_router_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "ts_router": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "ts_moe_gate_up_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                           _c_int, _c_int, _c_float, _c_float, _c_void_p],
-    "ts_moe_down_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "ts_moe_plan": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+                           _c_int, _c_int, _c_float, _c_float, _c_int, _c_void_p],
+    "ts_moe_down_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "ts_moe_gate_up": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "ts_moe_down": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
@@ -693,10 +693,33 @@ def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormaliz
 MOE_MMA = _os.environ.get("TS_MOE_MMA", "1") != "0"
 
 
-def moe_plan(ids: torch.Tensor, num_experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def moe_on_tensor_cores(dtype: torch.dtype, *inner_widths: int) -> bool:
+    """Whether the expert products of these inner widths run on the tensor-core kernels."""
+    return MOE_MMA and dtype == torch.bfloat16 and all(k % 8 == 0 for k in inner_widths)
+
+
+_moe_mma_tiles: Optional[tuple[int, int]] = None
+MOE_FEW_ROWS_PER_EXPERT = 12  # up to this many pairs per expert on average the short row tiles are planned
+
+
+def moe_row_tile(tensor_cores: bool, pairs: int = 0, num_experts: int = 1) -> int:
+    """Places per row tile of the expert products' kernels: what a plan is made for.  The tensor-core
+    kernels come in two shapes, for many rows per expert and for few (a function of the token count
+    alone, so a captured step keeps its shape)."""
+    global _moe_mma_tiles
+    if not tensor_cores:
+        return MOE_ROW_TILE
+    if _moe_mma_tiles is None:
+        fn = library().ts_moe_mma_row_tile
+        fn.argtypes, fn.restype = [_c_int], _c_int
+        _moe_mma_tiles = (int(fn(0)), int(fn(1)))
+    return _moe_mma_tiles[1] if pairs <= MOE_FEW_ROWS_PER_EXPERT * num_experts else _moe_mma_tiles[0]
+
+
+def moe_plan(ids: torch.Tensor, num_experts: int, tile_rows: int = MOE_ROW_TILE) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:
     """Sorts the (token, choice) pairs of ids [T, top] by expert on the device.  Returns offsets
     [E+1] (expert e's places are offsets[e]..offsets[e+1]), tile_offsets [E+1] (its first row tile of
-    MOE_ROW_TILE places) and order [T*top] (place -> pair index token*top + choice)."""
+    `tile_rows` places), order [T*top] (place -> pair index token*top + choice), and tile_rows."""
     flush_gemm_chain()
     _cuda_contig("ids", ids, torch.int32)
     if num_experts > MOE_MAX_EXPERTS:
@@ -704,16 +727,28 @@ def moe_plan(ids: torch.Tensor, num_experts: int) -> tuple[torch.Tensor, torch.T
     P = ids.numel()
     plan = torch.empty(2 * (num_experts + 1) + P, dtype=torch.int32, device=ids.device)
     offsets, tile_offsets, order = plan[: num_experts + 1], plan[num_experts + 1 : 2 * (num_experts + 1)], plan[2 * (num_experts + 1) :]
-    _check("moe_plan", _fn("ts_moe_plan")(ids.data_ptr(), P, int(num_experts), offsets.data_ptr(), tile_offsets.data_ptr(), order.data_ptr(), _stream()))
-    return offsets, tile_offsets, order
+    _check("moe_plan", _fn("ts_moe_plan")(ids.data_ptr(), P, int(num_experts), int(tile_rows), offsets.data_ptr(), tile_offsets.data_ptr(),
+                                          order.data_ptr(), _stream()))
+    return offsets, tile_offsets, order, int(tile_rows)
 
 
-def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple[torch.Tensor, torch.Tensor, torch.Tensor], gate: torch.Tensor,
+def _moe_path(name: str, plan, dtype: torch.dtype, *inner_widths: int) -> bool:
+    """True: the tensor-core kernel; the plan's row tile decides, and must suit the kernel it names."""
+    if plan[3] == MOE_ROW_TILE:
+        return False
+    if moe_on_tensor_cores(dtype, *inner_widths):
+        moe_row_tile(True)
+        if plan[3] in _moe_mma_tiles:
+            return True
+    raise KernelError(f"{name}: the plan was made for row tiles of {plan[3]}, which no kernel for {dtype} and inner widths {inner_widths} takes")
+
+
+def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple, gate: torch.Tensor,
                 up: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float) -> None:
     """For every pair, in the plan's order: act[place] = capped_glu(gate_e (w x[token]), up_e (w x[token])).
     x [T, K]; pair_weight [T*top] f32; gate, up [E, I, K]; act [T*top, I]."""
     flush_gemm_chain()
-    offsets, tile_offsets, order = plan
+    offsets, tile_offsets, order, _ = plan
     _cuda_contig("x", x)
     _cuda_contig("gate", gate, x.dtype)
     _cuda_contig("up", up, x.dtype)
@@ -724,20 +759,20 @@ def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple[torch.Te
     P = T * top
     if K2 != K or up.shape != gate.shape or act.shape != (P, I) or pair_weight.numel() != P or order.numel() != P:
         raise KernelError(f"moe_gate_up: shapes disagree: x {tuple(x.shape)}, gate {tuple(gate.shape)}, up {tuple(up.shape)}, act {tuple(act.shape)}")
-    if MOE_MMA and x.dtype == torch.bfloat16 and K % 8 == 0:
+    if _moe_path("moe_gate_up", plan, x.dtype, K):
         _check("moe_gate_up", _fn("ts_moe_gate_up_mma")(
             x.data_ptr(), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), gate.data_ptr(),
-            up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), _stream()))
+            up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), plan[3], _stream()))
         return
     _check("moe_gate_up", _fn("ts_moe_gate_up")(
         x.data_ptr(), _act_code("x", x), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(),
         gate.data_ptr(), up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), _stream()))
 
 
-def moe_down(act: torch.Tensor, plan: tuple[torch.Tensor, torch.Tensor, torch.Tensor], down: torch.Tensor, pair_out: torch.Tensor) -> None:
+def moe_down(act: torch.Tensor, plan: tuple, down: torch.Tensor, pair_out: torch.Tensor) -> None:
     """pair_out[pair] = down_e act[place] for every place of the plan.  act [P, I]; down [E, N, I]; pair_out [P, N]."""
     flush_gemm_chain()
-    offsets, tile_offsets, order = plan
+    offsets, tile_offsets, order, _ = plan
     _cuda_contig("act", act)
     _cuda_contig("down", down, act.dtype)
     _cuda_contig("pair_out", pair_out, act.dtype)
@@ -745,10 +780,10 @@ def moe_down(act: torch.Tensor, plan: tuple[torch.Tensor, torch.Tensor, torch.Te
     E, N, I2 = down.shape
     if I2 != I or pair_out.shape != (P, N) or order.numel() != P:
         raise KernelError(f"moe_down: shapes disagree: act {tuple(act.shape)}, down {tuple(down.shape)}, pair_out {tuple(pair_out.shape)}")
-    if MOE_MMA and act.dtype == torch.bfloat16 and I % 8 == 0:
+    if _moe_path("moe_down", plan, act.dtype, I):
         _check("moe_down", _fn("ts_moe_down_mma")(
             act.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), down.data_ptr(), pair_out.data_ptr(), P, E, I, N,
-            _stream()))
+            plan[3], _stream()))
         return
     _check("moe_down", _fn("ts_moe_down")(
         act.data_ptr(), _act_code("act", act), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), down.data_ptr(),
@@ -817,14 +852,21 @@ def _latent_mma_fns(rank: int, rot_dim: int):
 
 
 def latent_attention_splits(device: torch.device, num_seqs: int, rows_per_seq: int, plan_context: int, rank: int, rot_dim: int) -> int:
-    """Into how many key ranges a step of few rows per sequence cuts each sequence's keys, so that about
-    two CTAs per SM run: a function of the batch's size and the planned context only (a captured
-    step is replayed for every length), never more ranges than key blocks."""
+    """Into how many key ranges a step of few rows per sequence cuts each sequence's keys: the count
+    that needs the fewest key blocks one after the other on an SM, given that one CTA is resident per
+    SM: rounds of CTAs times (blocks per range + about a block and a half of fixed cost: the query
+    rows, the first copy's latency, the partial sums).  A function of the batch's size and the
+    planned context only (a captured step is replayed for every length)."""
     _, rows, keys = _latent_mma_fns(rank, rot_dim)
     ctas = max(1, num_seqs * -(-rows_per_seq // rows))
-    by_work = -(-2 * _sm_count(device) // ctas)
-    by_keys = max(1, plan_context // keys)
-    return max(1, min(by_work, by_keys, LATENT_MMA_MAX_SPLITS))
+    blocks = max(1, -(-plan_context // keys))
+    sms = _sm_count(device)
+    best, best_cost = 1, None
+    for splits in range(1, min(blocks, LATENT_MMA_MAX_SPLITS) + 1):
+        cost = -(-ctas * splits // sms) * (-(-blocks // splits) + 1.5) + (0.5 if splits > 1 else 0.0)  # + the merge kernel
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = splits, cost
+    return best
 
 
 def latent_attention_mma(q_abs: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gates: Optional[torch.Tensor],

@@ -146,7 +146,9 @@ class RoutedExperts(FeedForward):
         chosen = torch.empty((T, top), device=dev, dtype=torch.int32)
         weights = torch.empty((T, top), device=dev, dtype=torch.float32)
         ops.router(rows, self.router, top, self.renormalize, chosen, weights)
-        plan = ops.moe_plan(chosen, self.num_experts)
+        # both products take the same plan: the tensor cores only if both inner widths suit them
+        tensor_cores = ops.moe_on_tensor_cores(x.dtype, self.hidden_size, self.intermediate_size)
+        plan = ops.moe_plan(chosen, self.num_experts, ops.moe_row_tile(tensor_cores, T * top, self.num_experts))
         act = torch.empty((T * top, self.intermediate_size), device=dev, dtype=x.dtype)
         on_input = self.weight_on == "input"
         ones = None if on_input else torch.ones((T * top,), device=dev, dtype=torch.float32)
