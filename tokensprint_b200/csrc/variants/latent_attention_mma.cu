@@ -53,6 +53,9 @@ __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
 __device__ __forceinline__ void ldmatrix_x2_trans(unsigned (&r)[2], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
 }
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -99,6 +102,7 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
     lo_row[i] = window > 0 ? pos_row[i] - window + 1 : 0;
   }
 
+  const bool group_active = r0 + rg * 16 < rows_b;
   if (my_lo > my_hi) {  // nothing in this split's range: an empty partial
     if (splits > 1 && vq == 0 && qi == 0)
       for (int i = 0; i < 2; ++i)
@@ -110,19 +114,19 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
   }
 
   const int* table = block_table + (size_t)b * max_blocks;
+  // four threads copy one cached row (THREADS = 4 * BN): the page lookup is done once per row
+  static_assert(THREADS == 4 * BN, "one cached row per four threads");
   auto load_keys = [&](int kb, int buf) {
-    __nv_bfloat16* dst = Ks + (size_t)buf * BN * DS;
     constexpr int CH = D / 8;
-    for (int c = threadIdx.x; c < BN * CH; c += THREADS) {
-      const int key = c / CH, part = c - key * CH;
-      const int j = kb * BN + key;
-      __nv_bfloat16* d = dst + (size_t)key * DS + part * 8;
-      if (j >= k_lo && j <= k_hi) {
-        const size_t slot = (size_t)table[j / page] * page + (j % page);
-        cp_async16(d, cache + slot * D + part * 8);
-      } else {
-        *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
-      }
+    const int key = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    const int j = kb * BN + key;
+    __nv_bfloat16* d = Ks + ((size_t)buf * BN + key) * DS;
+    if (j >= k_lo && j <= k_hi) {
+      const __nv_bfloat16* src = cache + ((size_t)table[j / page] * page + (j % page)) * D;
+#pragma unroll 6
+      for (int part = sub; part < CH; part += 4) cp_async16(d + part * 8, src + part * 8);
+    } else {
+      for (int part = sub; part < CH; part += 4) *reinterpret_cast<uint4*>(d + part * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
   };
   {  // the query rows, with the first key block
@@ -155,6 +159,7 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
       cp_async_wait<0>();
     }
     __syncthreads();
+    if (group_active) {  // a row group without rows (a decode step of few heads) only helps with the copies
     const __nv_bfloat16* Kb = Ks + (size_t)buf * BN * DS;
 
     // S: this warp's 16 rows against its 16 keys.  Even and odd k-steps add into sums of their own, so
@@ -244,14 +249,28 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
       unsigned a[4];
       ldmatrix_x4(a, Pg + (size_t)(lane & 15) * PS + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
-      for (int i = 0; i < VT_W; ++i) {
+      for (int i = 0; i + 1 < VT_W; i += 2) {  // two value tiles per load where both exist
         const int tile = vq * VT_W + i;
-        if (tile < VT) {
+        if (tile + 1 < VT) {
+          unsigned vf[4];  // keys 0-7 / 8-15 of tile, then of tile + 1
+          ldmatrix_x4_trans(vf, Kb + (size_t)(kk * 16 + (lane & 15)) * DS + tile * 8 + (lane >> 4) * 8);
+          mma_bf16(o[i], a, vf[0], vf[1]);
+          mma_bf16(o[i + 1], a, vf[2], vf[3]);
+        } else if (tile < VT) {
           unsigned vf[2];
           ldmatrix_x2_trans(vf, Kb + (size_t)(kk * 16 + (lane & 15)) * DS + tile * 8);
           mma_bf16(o[i], a, vf[0], vf[1]);
         }
       }
+      if (VT_W & 1) {
+        const int tile = vq * VT_W + VT_W - 1;
+        if (tile < VT) {
+          unsigned vf[2];
+          ldmatrix_x2_trans(vf, Kb + (size_t)(kk * 16 + (lane & 15)) * DS + tile * 8);
+          mma_bf16(o[VT_W - 1], a, vf[0], vf[1]);
+        }
+      }
+    }
     }
     __syncthreads();  // the buffer and P are written again in the next round
   }
