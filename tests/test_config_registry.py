@@ -109,7 +109,8 @@ def test_listing_script():
     import model_registry
 
     out = model_registry.listing()
-    assert out.startswith("Registered models:\n\nqwen:\n")
+    assert out.startswith("Registered models:\n\nfegetar:\n") and "\n\nqwen:\n" in out  # families in alphabetical order
+    assert "  - fegetar-w2048 (fegetar/fegetar-w2048)" in out
     assert "  - qwen3-0.6b (qwen/qwen3-0.6b)" in out
     for name in ("qwen3-1.7b", "qwen3-4b", "qwen3-8b", "qwen3-14b", "qwen3-32b"):
         assert f"  - {name} (qwen/{name})" in out

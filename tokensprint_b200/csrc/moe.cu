@@ -316,7 +316,7 @@ TS_EXPORT int ts_moe_combine(const void* pair_out, const void* shared, void* out
 // residual rows or as their rounding in the compute type) and every warp walks expert rows with
 // 16-byte loads, so a router row is read once per RT tokens.  A logit's sum runs over the width
 // in a fixed order (lane-strided partial sums, then the warp's tree): it does not depend on the
-// tokens beside it.
+// tokens beside it, nor on how many tokens a CTA takes.
 #define ROUTER_MAX_TOKENS 4
 
 template <typename TX>
@@ -335,11 +335,28 @@ __global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, c
   for (int e = warp; e < E; e += nwarps) {
     const float* row = router + (size_t)e * W;
     float acc[ROUTER_MAX_TOKENS] = {0.f, 0.f, 0.f, 0.f};
-    for (int k = lane; k < W; k += 32) {
-      const float w = row[k];
+    if ((W & 3) == 0) {  // 16-byte loads, several in flight: a step of few tokens is a chain of such loads and little else
+      const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+      for (int k = lane; k < (W >> 2); k += 32) {
+        const float4 w = row4[k];
 #pragma unroll
-      for (int j = 0; j < ROUTER_MAX_TOKENS; ++j)
-        if (j < nt) acc[j] = fmaf(xs[(size_t)j * W + k], w, acc[j]);
+        for (int j = 0; j < ROUTER_MAX_TOKENS; ++j)
+          if (j < nt) {
+            const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)j * W + 4 * k);
+            acc[j] = fmaf(xv.x, w.x, acc[j]);
+            acc[j] = fmaf(xv.y, w.y, acc[j]);
+            acc[j] = fmaf(xv.z, w.z, acc[j]);
+            acc[j] = fmaf(xv.w, w.w, acc[j]);
+          }
+      }
+    } else {
+      for (int k = lane; k < W; k += 32) {
+        const float w = row[k];
+#pragma unroll
+        for (int j = 0; j < ROUTER_MAX_TOKENS; ++j)
+          if (j < nt) acc[j] = fmaf(xs[(size_t)j * W + k], w, acc[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < ROUTER_MAX_TOKENS; ++j) {
@@ -390,7 +407,9 @@ TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, int T, 
                         float* weights, void* stream) {
   if (T <= 0) return 0;
   if (W <= 0 || E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
-  int rt = ROUTER_MAX_TOKENS;
+  // tokens per CTA: four where there are CTAs enough for every SM several times over (a router row is
+  // then read once per four tokens), fewer in steps of few tokens (more CTAs, shorter chains of loads)
+  int rt = T >= 2048 ? ROUTER_MAX_TOKENS : (T >= 512 ? 2 : 1);
   while (rt > 1 && (size_t)rt * (W + E) * sizeof(float) > 200 * 1024) rt >>= 1;
   const size_t smem = (size_t)rt * (W + E) * sizeof(float);
   if (smem > 227 * 1024) return TS_ERR_UNSUPPORTED_SIZE;

@@ -27,7 +27,7 @@ from pathlib import Path
 from typing import Any, Optional
 
 from tokensprint_b200.config.model_config import ConfigError, read_config_json, require, write_config_json
-from tokensprint_b200.config.registry import register_architecture
+from tokensprint_b200.config.registry import PRESET_DIR, register_architecture, register_preset
 from tokensprint_b200.models.spec import ModelSpec
 from tokensprint_b200.parts.base import PartSpec
 
@@ -244,3 +244,9 @@ def build_fegetar_spec(config: FegetarConfig) -> ModelSpec:
         vocab_size=config.vocab, hidden_size=W, embedding="embed", layers=layers, final_norm=norm("final.norm", 1.0), lm_head="head",
         max_positions=config.max_position_embeddings, eos_token_id=config.eos_token_id, ignorable_tensors=tuple(ignorable),
         embedding_transform=pair)
+
+
+# A named model of this design, so that the command lines can run it with random weights: four
+# layers at a width of 2,048 (dense and routed feed-forwards in turn), the size bench.py --designs times.
+for _path in sorted(PRESET_DIR.glob("fegetar-*.json")):
+    register_preset("fegetar", _path.stem, _path)
