@@ -404,9 +404,14 @@ def run_probe(args) -> int:
     from tokensprint_b200.engine.runner import ModelRunner, StepEntry
     from tokensprint_b200.models.api import random_model
 
-    d = get_preset_dict(MODEL_NAME)
-    d["num_hidden_layers"] = args.layers or 4
-    cfg = Qwen3Config.from_dict(d)
+    if args.designs:  # the other design's named model (four layers at width 2,048)
+        from tokensprint_b200.config.registry import get_model_config
+
+        cfg = get_model_config("fegetar-w2048")
+    else:
+        d = get_preset_dict(MODEL_NAME)
+        d["num_hidden_layers"] = args.layers or 4
+        cfg = Qwen3Config.from_dict(d)
     model = random_model(cfg, seed=0, dtype="bfloat16", generate_on_device=True)
     batch = args.batch
     runner = ModelRunner(model, page_size=PAGE_SIZE, num_pages=batch * 80 + 400, num_slots=batch + 2,
@@ -741,7 +746,7 @@ def main() -> int:
                    help="Fegetar beside Qwen3 dense at equal size (a few layers of realistic widths, random weights): prompt and "
                         "decode throughput and the attention kernels against their rooflines (one JSON line)")
     p.add_argument("--probe", choices=["decode", "prefill"], default=None,
-                   help="run a few steps inside cudaProfilerStart/Stop for ncu and exit (see profiles/)")
+                   help="run a few steps inside cudaProfilerStart/Stop for ncu and exit (see profiles/); with --designs: of Fegetar's named model")
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

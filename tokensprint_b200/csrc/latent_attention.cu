@@ -19,10 +19,12 @@
 #define LAT_PAIR_HALF 0         // entry j turns with entry j + dims/2
 #define LAT_PAIR_NEIGHBOURS 1   // entry 2i turns with entry 2i + 1
 
-// One entry of a rotated vector: x[j] after the turn by position * inv_freq[pair].
+#define LAT_MAX_PAIRS 512
+
+// One entry of a rotated vector: x[j] after the turn by the token's angle of its pair, whose
+// cosine and sine are cs[pair].
 template <typename TA>
-__device__ __forceinline__ float lat_rotated(const TA* __restrict__ x, int j, int dims, int pairing, float pos,
-                                             const float* __restrict__ inv_freq) {
+__device__ __forceinline__ float lat_rotated(const TA* __restrict__ x, int j, int dims, int pairing, const float2* __restrict__ cs) {
   const float v = ts_to_float(x[j]);
   if (j >= dims) return v;  // behind the rotated entries
   int pair, partner;
@@ -37,10 +39,8 @@ __device__ __forceinline__ float lat_rotated(const TA* __restrict__ x, int j, in
     pair = first ? j : j - half;
     partner = first ? j + half : j - half;
   }
-  float sn, cs;
-  sincosf(pos * inv_freq[pair], &sn, &cs);
   const float w = ts_to_float(x[partner]);
-  return first ? v * cs - w * sn : v * cs + w * sn;
+  return first ? v * cs[pair].x - w * cs[pair].y : v * cs[pair].x + w * cs[pair].y;
 }
 
 template <typename TA>
@@ -51,9 +51,15 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
                                       int H, int nope, int rot, int rank) {
   ts_pdl_prologue();
   __shared__ float scratch[33];
+  __shared__ float2 cs[LAT_MAX_PAIRS];  // (cos, sin) of the token's angles, shared by the key part and every head
   const int t = blockIdx.x;
   const TA* row = proj + (size_t)t * ld;
   const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {
+    float sn, c;
+    sincosf(pos * inv_freq[i], &sn, &c);
+    cs[i] = make_float2(c, sn);
+  }  // the block-wide sum below has a barrier before anyone reads the table
   const int slot = slot_mapping ? slot_mapping[t] : -1;
   const int key_dim = rank + rot;
   // the latent: RMS norm with a plain weight
@@ -69,13 +75,13 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
     TA* dst = cache + (size_t)slot * key_dim;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = ts_from_float<TA>(ts_to_float(lat[i]) * rstd * latent_weight[i]);
     for (int j = threadIdx.x; j < rot; j += blockDim.x)
-      dst[rank + j] = ts_from_float<TA>(lat_rotated(lat + rank, j, rot_dims, pairing, pos, inv_freq));
+      dst[rank + j] = ts_from_float<TA>(lat_rotated(lat + rank, j, rot_dims, pairing, cs));
   }
   // every head's rotated query part, behind the place of its absorbed part
   for (int i = threadIdx.x; i < H * rot; i += blockDim.x) {
     const int a = i / rot, j = i - a * rot;
     const TA* qr = row + q_off + (size_t)a * (nope + rot) + nope;
-    q_abs[((size_t)t * H + a) * key_dim + rank + j] = ts_from_float<TA>(lat_rotated(qr, j, rot_dims, pairing, pos, inv_freq));
+    q_abs[((size_t)t * H + a) * key_dim + rank + j] = ts_from_float<TA>(lat_rotated(qr, j, rot_dims, pairing, cs));
   }
   if (gates)
     for (int a = threadIdx.x; a < H; a += blockDim.x) gates[(size_t)t * H + a] = 1.f / (1.f + expf(-ts_to_float(row[gate_off + a])));
@@ -86,6 +92,7 @@ TS_EXPORT int ts_latent_prepare(const void* proj, int act_dtype, long long ld, i
                                 const float* inv_freq, int rot_dims, int pairing, float* gates, int T, int H, int nope, int rot,
                                 int rank, void* stream) {
   if (T <= 0) return 0;
+  if (rot_dims > 2 * LAT_MAX_PAIRS) return TS_ERR_UNSUPPORTED_SIZE;
   if (H <= 0 || nope < 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || (rot_dims > 0 && !inv_freq) ||
       (pairing != LAT_PAIR_HALF && pairing != LAT_PAIR_NEIGHBOURS))
     return TS_ERR_BAD_ARGUMENT;

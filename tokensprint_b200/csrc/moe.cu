@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, c
     float acc[ROUTER_MAX_TOKENS] = {0.f, 0.f, 0.f, 0.f};
     if ((W & 3) == 0) {  // 16-byte loads, several in flight: a step of few tokens is a chain of such loads and little else
       const float4* row4 = reinterpret_cast<const float4*>(row);
-#pragma unroll 4
+#pragma unroll 8
       for (int k = lane; k < (W >> 2); k += 32) {
         const float4 w = row4[k];
 #pragma unroll

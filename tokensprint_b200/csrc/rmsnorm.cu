@@ -181,18 +181,73 @@ __global__ void rmsnorm_add_kernel(const TB* __restrict__ branch, const float* _
   }
 }
 
+// The same for widths that are a multiple of 4: the branch row and the stream's row stay in
+// registers between the sum of squares and the update, so each is read once, with 16-byte loads
+// issued back to back.
+template <typename TB, typename TO>
+__global__ void rmsnorm_add_vec_kernel(const TB* __restrict__ branch, const float* __restrict__ weight, float* __restrict__ hidden,
+                                       TO* __restrict__ rounded, int H, float eps) {
+  ts_pdl_prologue();
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const TB* b = branch + (size_t)row * H;
+  float* h = hidden + (size_t)row * H;
+  const int chunks = H >> 2;
+  float4 bv[RN_MAX_CHUNKS], hv[RN_MAX_CHUNKS];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      bv[k] = ts_load4(b + 4 * c);
+      hv[k] = ts_load4(h + 4 * c);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) ss += bv[k].x * bv[k].x + bv[k].y * bv[k].y + bv[k].z * bv[k].z + bv[k].w * bv[k].w;
+  }
+  ss = ts_block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      const float4 w = ts_load4(weight + 4 * c);
+      const float4 v = make_float4(hv[k].x + bv[k].x * rstd * w.x, hv[k].y + bv[k].y * rstd * w.y, hv[k].z + bv[k].z * rstd * w.z,
+                                   hv[k].w + bv[k].w * rstd * w.w);
+      ts_store4(h + 4 * c, v);
+      if (rounded) ts_store4(rounded + (size_t)row * H + 4 * c, v);
+    }
+  }
+}
+
+template <typename TB, typename TO>
+static int launch_rmsnorm_add(const void* branch, const float* weight, float* hidden, void* rounded, int rows, int H, float eps, cudaStream_t s) {
+  const int chunks = H >> 2;
+  const bool aligned = (H % 4 == 0) && (((uintptr_t)branch | (uintptr_t)weight | (uintptr_t)hidden | (uintptr_t)rounded) % 16 == 0);
+  if (aligned && chunks <= RN_MAX_CHUNKS * 1024) {
+    int threads = (chunks + RN_MAX_CHUNKS - 1) / RN_MAX_CHUNKS;
+    if (rows <= 512) threads = chunks;  // few rows: one piece per thread, shortest latency
+    threads = min(1024, max(32, (threads + 31) / 32 * 32));
+    return ts_launch(rmsnorm_add_vec_kernel<TB, TO>, dim3(rows), dim3(threads), 0, s, (const TB*)branch, weight, hidden, (TO*)rounded, H, eps);
+  }
+  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
+  return ts_launch(rmsnorm_add_kernel<TB, TO>, dim3(rows), dim3(threads), 0, s, (const TB*)branch, weight, hidden, (TO*)rounded, H, eps);
+}
+
 TS_EXPORT int ts_rmsnorm_add(const void* branch, int branch_dtype, const float* weight, float* hidden, void* rounded, int rounded_dtype,
                              int rows, int H, float eps, void* stream) {
   if (rows <= 0) return 0;
   if (H <= 0) return TS_ERR_BAD_ARGUMENT;
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
   if (branch_dtype == TS_DTYPE_F32 && (rounded == nullptr || rounded_dtype == TS_DTYPE_F32))
-    return ts_launch(rmsnorm_add_kernel<float, float>, dim3(rows), dim3(threads), 0, s, (const float*)branch, weight, hidden, (float*)rounded, H, eps);
+    return launch_rmsnorm_add<float, float>(branch, weight, hidden, rounded, rows, H, eps, s);
   if (branch_dtype == TS_DTYPE_F32 && rounded_dtype == TS_DTYPE_BF16)
-    return ts_launch(rmsnorm_add_kernel<float, __nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (const float*)branch, weight, hidden, (__nv_bfloat16*)rounded, H, eps);
+    return launch_rmsnorm_add<float, __nv_bfloat16>(branch, weight, hidden, rounded, rows, H, eps, s);
   if (branch_dtype == TS_DTYPE_BF16 && (rounded == nullptr || rounded_dtype == TS_DTYPE_BF16))
-    return ts_launch(rmsnorm_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (const __nv_bfloat16*)branch, weight, hidden, (__nv_bfloat16*)rounded, H, eps);
+    return launch_rmsnorm_add<__nv_bfloat16, __nv_bfloat16>(branch, weight, hidden, rounded, rows, H, eps, s);
   return TS_ERR_BAD_ARGUMENT;
 }
 

@@ -138,6 +138,14 @@ class FegetarConfig:
         if self.bigram_buckets < 0 or self.side_dim < 0:
             raise ConfigError("config.json: 'embedding.bigram.buckets' and 'token_side.dim' must not be negative")
 
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def hidden_size(self) -> int:
+        return self.width
+
     @classmethod
     def from_dict(cls, d: dict[str, Any]) -> "FegetarConfig":
         layers = []
