@@ -82,7 +82,7 @@ def test_pair_hash_embedding_takes_large_multipliers():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [72, 256, 1000])
+@pytest.mark.parametrize("width", [70, 72, 256, 1000, 4100])
 def test_norm_on_the_branch(dtype, width):
     from tokensprint_b200 import ops
 
@@ -283,7 +283,7 @@ def test_router_picks_by_score_and_breaks_ties_by_index():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T, W, E, top", [(1, 72, 7, 3), (9, 256, 12, 1), (130, 1000, 33, 4)])
+@pytest.mark.parametrize("T, W, E, top", [(1, 72, 7, 3), (9, 256, 12, 1), (130, 1000, 33, 4), (5, 70, 4, 4), (600, 128, 9, 2), (2100, 64, 5, 1)])
 def test_router_in_one_kernel(dtype, T, W, E, top):
     from tokensprint_b200 import ops
 

@@ -309,25 +309,46 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(
 }
 
 // Merges the splits of every row: weights exp2((m_s - max m) * scale), sums of the unnormalised
-// rows and of their sums, one division, the gate.
+// rows and of their sums, one division, the gate.  The splits' maxima and sums are fetched by one
+// thread each (all loads in flight at once) and turned into weights by the first warp; every
+// thread then sums its columns with several loads in flight.
+constexpr int MERGE_MAX_SPLITS = 64;
+
 __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_m,
                                               const float* __restrict__ part_l, __nv_bfloat16* __restrict__ out,
                                               const float* __restrict__ gates, int splits, long long total_rows, float scale_log2) {
   ts_pdl_prologue();
+  __shared__ float weight[MERGE_MAX_SPLITS];
+  __shared__ float factor;
   const long long row = blockIdx.x;
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_m[(size_t)s * total_rows + row]);
-  float l = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_m[(size_t)s * total_rows + row];
-    if (ms != -INFINITY) l += exp2f((ms - m) * scale_log2) * part_l[(size_t)s * total_rows + row];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (lane < splits) {
+      m0 = part_m[(size_t)lane * total_rows + row];
+      l0 = part_l[(size_t)lane * total_rows + row];
+    }
+    if (lane + 32 < splits) {
+      m1 = part_m[(size_t)(lane + 32) * total_rows + row];
+      l1 = part_l[(size_t)(lane + 32) * total_rows + row];
+    }
+    const float g = gates ? gates[row] : 1.f;
+    const float m = ts_warp_max(fmaxf(m0, m1));
+    const float w0 = (lane < splits && m0 != -INFINITY) ? exp2f((m0 - m) * scale_log2) : 0.f;
+    const float w1 = (lane + 32 < splits && m1 != -INFINITY) ? exp2f((m1 - m) * scale_log2) : 0.f;
+    const float l = ts_warp_sum(w0 * l0 + w1 * l1);
+    weight[lane] = w0;
+    weight[lane + 32] = w1;
+    if (lane == 0) factor = l > 0.f ? g / l : 0.f;
   }
-  const float f = l > 0.f ? (gates ? gates[row] : 1.f) / l : 0.f;
+  __syncthreads();
+  const float f = factor;
   for (int c = threadIdx.x; c < RANK; c += blockDim.x) {
     float acc = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
-      const float ms = part_m[(size_t)s * total_rows + row];
-      if (ms != -INFINITY) acc += exp2f((ms - m) * scale_log2) * part_o[((size_t)s * total_rows + row) * RANK + c];
+      const float w = weight[s];
+      if (w != 0.f) acc += w * part_o[((size_t)s * total_rows + row) * RANK + c];  // an empty range left nothing to read
     }
     out[(size_t)row * RANK + c] = __float2bfloat16_rn(acc * f);
   }
@@ -346,7 +367,7 @@ TS_EXPORT int ts_latent_attention_mma(const void* q_abs, const void* cache, void
                                       int max_seqlen_q, int T, int H, float scale, int window, int splits, float* scratch, void* stream) {
   if (num_seqs <= 0 || T <= 0) return 0;
   if (H <= 0 || page <= 0 || max_blocks <= 0 || max_seqlen_q <= 0 || splits < 1 || (splits > 1 && !scratch)) return TS_ERR_BAD_ARGUMENT;
-  if (SMEM_BYTES > 227 * 1024 || num_seqs > 65535 || splits > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  if (SMEM_BYTES > 227 * 1024 || num_seqs > 65535 || splits > MERGE_MAX_SPLITS) return TS_ERR_UNSUPPORTED_SIZE;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
