@@ -39,16 +39,17 @@ __device__ __forceinline__ int tile_expert(const int* __restrict__ tile_offsets,
   return lo;
 }
 
-// WM x WN warps: a warp owns 16 rows and NB / WN of the 128 weight rows in shared memory.  GATE_UP: the
-// first half of a warp's weight rows are gate rows and the second half the up rows of the same
-// outputs (so both operands of an activation sit in one thread); else 128 rows of one matrix.
-template <bool GATE_UP, int WM, int WN, int STAGES>
+// WM x WN warps: a warp owns MT tiles of 16 rows and NB / WN of the 128 weight rows in shared memory
+// (the more of both, the fewer shared-memory loads per MMA: MT + NT / 2 loads feed MT * NT MMAs).
+// GATE_UP: the first half of a warp's weight rows are gate rows and the second half the up rows of
+// the same outputs (so both operands of an activation sit in one thread); else 128 rows of one matrix.
+template <bool GATE_UP, int WM, int WN, int MT, int STAGES>
 __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const float* __restrict__ pair_weight,
                                                                const int* __restrict__ order, const int* __restrict__ offsets,
                                                                const int* __restrict__ tile_offsets, const __nv_bfloat16* __restrict__ B0,
                                                                const __nv_bfloat16* __restrict__ B1, __nv_bfloat16* __restrict__ out, int E,
                                                                int K, int NOUT, int top, float limit, float alpha) {
-  constexpr int BM = 16 * WM, THREADS = 32 * WM * WN, CW = NB / WN, HALF = CW / 2, NT = CW / 8;
+  constexpr int BM = 16 * MT * WM, THREADS = 32 * WM * WN, CW = NB / WN, HALF = CW / 2, NT = CW / 8;
   constexpr size_t STAGE_ELEMS = (size_t)(BM + NB) * KS;
   ts_pdl_prologue();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -105,85 +106,103 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, qi = lane & 3;
   const int wm = warp / WN, wn = warp % WN;
-  float acc[NT][4];
+  float acc[MT][NT][4];
 #pragma unroll
-  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[m][i][0] = acc[m][i][1] = acc[m][i][2] = acc[m][i][3] = 0.f;
 
   for (int kt = 0; kt < nk; ++kt) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
     if (kt + STAGES - 1 < nk) load_stage(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
-    const __nv_bfloat16* As = smem + (size_t)(kt % STAGES) * STAGE_ELEMS;
-    const __nv_bfloat16* Bs = As + (size_t)BM * KS + (size_t)wn * CW * KS;
+    const __nv_bfloat16* As = smem + (size_t)(kt % STAGES) * STAGE_ELEMS + (size_t)wm * 16 * MT * KS;
+    const __nv_bfloat16* Bs = smem + (size_t)(kt % STAGES) * STAGE_ELEMS + (size_t)BM * KS + (size_t)wn * CW * KS;
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
-      unsigned a[4];
-      ldmatrix_x4(a, As + (size_t)(wm * 16 + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8);
+      unsigned a[MT][4];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) ldmatrix_x4(a[m], As + (size_t)(m * 16 + (lane & 15)) * KS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int nb = 0; nb < NT / 2; ++nb) {
         unsigned b[4];
         ldmatrix_x4(b, Bs + (size_t)(nb * 16 + (lane >> 4) * 8 + (lane & 7)) * KS + ks * 16 + ((lane >> 3) & 1) * 8);
-        mma_bf16(acc[2 * nb], a, b[0], b[1]);
-        mma_bf16(acc[2 * nb + 1], a, b[2], b[3]);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          mma_bf16(acc[m][2 * nb], a[m], b[0], b[1]);
+          mma_bf16(acc[m][2 * nb + 1], a[m], b[2], b[3]);
+        }
       }
     }
   }
   cp_async_wait<0>();
 
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int rl = wm * 16 + quad + 8 * r;
-    const int pair = a_pair[rl];
-    if (pair < 0) continue;
-    if (GATE_UP) {
-      const float w = pair_weight[pair];
-      __nv_bfloat16* dst = out + (size_t)(row0 + rl) * NOUT;
+  for (int m = 0; m < MT; ++m)
 #pragma unroll
-      for (int nb = 0; nb < NT / 2; ++nb)
+    for (int r = 0; r < 2; ++r) {
+      const int rl = (wm * MT + m) * 16 + quad + 8 * r;
+      const int pair = a_pair[rl];
+      if (pair < 0) continue;
+      if (GATE_UP) {
+        const float w = pair_weight[pair];
+        __nv_bfloat16* dst = out + (size_t)(row0 + rl) * NOUT;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int n = n0 + wn * HALF + nb * 8 + 2 * qi + c;
-          if (n >= NOUT) continue;
-          // the sums are rounded to bfloat16 first, as a product stored to memory would be
-          const float gv = __bfloat162float(__float2bfloat16_rn(w * acc[nb][2 * r + c]));
-          const float uv = __bfloat162float(__float2bfloat16_rn(w * acc[nb + NT / 2][2 * r + c]));
-          const float a = fminf(gv, limit), b = fminf(fmaxf(uv, -limit), limit);
-          dst[n] = __float2bfloat16_rn(a / (1.f + expf(-alpha * a)) * (b + 1.f));
+        for (int nb = 0; nb < NT / 2; ++nb) {
+          const int n = n0 + wn * HALF + nb * 8 + 2 * qi;
+          float y[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            // the sums are rounded to bfloat16 first, as a product stored to memory would be
+            const float gv = __bfloat162float(__float2bfloat16_rn(w * acc[m][nb][2 * r + c]));
+            const float uv = __bfloat162float(__float2bfloat16_rn(w * acc[m][nb + NT / 2][2 * r + c]));
+            const float a = fminf(gv, limit), b = fminf(fmaxf(uv, -limit), limit);
+            y[c] = a / (1.f + expf(-alpha * a)) * (b + 1.f);
+          }
+          if (n + 1 < NOUT && (NOUT & 1) == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(y[0], y[1]);
+          } else {
+            if (n < NOUT) dst[n] = __float2bfloat16_rn(y[0]);
+            if (n + 1 < NOUT) dst[n + 1] = __float2bfloat16_rn(y[1]);
+          }
         }
-    } else {
-      __nv_bfloat16* dst = out + (size_t)pair * NOUT;
+      } else {
+        __nv_bfloat16* dst = out + (size_t)pair * NOUT;
 #pragma unroll
-      for (int nb = 0; nb < NT; ++nb)
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int n = n0 + wn * CW + nb * 8 + 2 * qi + c;
-          if (n < NOUT) dst[n] = __float2bfloat16_rn(acc[nb][2 * r + c]);
+        for (int nb = 0; nb < NT; ++nb) {
+          const int n = n0 + wn * CW + nb * 8 + 2 * qi;
+          if (n + 1 < NOUT && (NOUT & 1) == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(acc[m][nb][2 * r], acc[m][nb][2 * r + 1]);
+          } else {
+            if (n < NOUT) dst[n] = __float2bfloat16_rn(acc[m][nb][2 * r]);
+            if (n + 1 < NOUT) dst[n + 1] = __float2bfloat16_rn(acc[m][nb][2 * r + 1]);
+          }
         }
+      }
     }
-  }
 }
 
-// Two shapes: many rows per expert (tiles of 128 rows, 8 warps one above the other, 3 slices in
-// flight) and few (tiles of 16 rows, 4 warps side by side over the 128 weight rows, 3 slices in
+// Two shapes: many rows per expert (tiles of 128 rows, 2 x 4 warps of 64 rows x 32 weight rows each,
+// 3 slices in flight) and few (tiles of 16 rows, 4 warps side by side over the 128 weight rows, 3 slices in
 // flight, three CTAs per SM: the step then streams the chosen experts' weights and little else).
 constexpr int ROWS_MANY = 128, ROWS_FEW = 16;
 
-template <bool GATE_UP, int WM, int WN, int STAGES>
+template <bool GATE_UP, int WM, int WN, int MT, int STAGES>
 int launch(const void* A, const float* pair_weight, const int* order, const int* offsets, const int* tile_offsets, const void* B0,
            const void* B1, void* out, int P, int E, int K, int NOUT, int top, float limit, float alpha, cudaStream_t s) {
-  constexpr int BM = 16 * WM;
+  constexpr int BM = 16 * MT * WM;
   constexpr size_t SMEM_BYTES = (size_t)STAGES * (BM + NB) * KS * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(moe_mma_kernel<GATE_UP, WM, WN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(moe_mma_kernel<GATE_UP, WM, WN, MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int cols = GATE_UP ? NB / 2 : NB;
   const dim3 grid((NOUT + cols - 1) / cols, (P + BM - 1) / BM + E);
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(moe_mma_kernel<GATE_UP, WM, WN, STAGES>, grid, dim3(32 * WM * WN), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight,
+  return ts_launch(moe_mma_kernel<GATE_UP, WM, WN, MT, STAGES>, grid, dim3(32 * WM * WN), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight,
                    order, offsets, tile_offsets, (const __nv_bfloat16*)B0, (const __nv_bfloat16*)B1, (__nv_bfloat16*)out, E, K, NOUT, top,
                    limit, alpha);
 }
@@ -202,8 +221,8 @@ TS_EXPORT int ts_moe_gate_up_mma(const void* x, const float* pair_weight, const 
   if (E <= 0 || K <= 0 || I <= 0 || top <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (K % 8 || (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)up) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
   if (tile_rows == ROWS_MANY)
-    return launch<true, 8, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
-  return launch<true, 1, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
+    return launch<true, 2, 4, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
+  return launch<true, 1, 4, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
 }
 
 TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offsets, const int* tile_offsets, const void* down,
@@ -212,6 +231,6 @@ TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offs
   if (E <= 0 || I <= 0 || N <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (I % 8 || (((uintptr_t)act | (uintptr_t)down) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
   if (tile_rows == ROWS_MANY)
-    return launch<false, 8, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
-  return launch<false, 1, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
+    return launch<false, 2, 4, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
+  return launch<false, 1, 4, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
 }
