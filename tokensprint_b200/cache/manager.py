@@ -3,7 +3,8 @@
 Keys and values live in pages of `page_size` token positions.  Layers are sorted into
 *groups* by what they need: a "full" group keeps every key of a request, a "window"
 group may give a page back once every later query is further than `window` positions
-from all of the page's keys.  Each group has a pool of pages of its own (its own device
+from all of the page's keys, a "chunk" group (queries see only the keys of their own block
+of `window` positions, counted from position 0) once the next query lies in a later block.  Each group has a pool of pages of its own (its own device
 tensors, its own free list); a request holds one block table per group.  Beside the
 pages there are slots of fixed size for per-request state; a request takes one when it
 is admitted and gives it back with its pages (an architecture without such state still
@@ -38,14 +39,14 @@ class OutOfSlots(CacheError):
 
 @dataclass(frozen=True)
 class GroupSpec:
-    kind: str  # "full" or "window"
-    window: int = 0
+    kind: str  # "full", "window" or "chunk"
+    window: int = 0  # the window's length, or the length of a chunk group's blocks of positions
 
     def __post_init__(self) -> None:
-        if self.kind not in ("full", "window"):
-            raise ValueError(f"cache group kind must be 'full' or 'window', got {self.kind!r}")
-        if self.kind == "window" and self.window <= 0:
-            raise ValueError("a window group needs a positive window")
+        if self.kind not in ("full", "window", "chunk"):
+            raise ValueError(f"cache group kind must be 'full', 'window' or 'chunk', got {self.kind!r}")
+        if self.kind != "full" and self.window <= 0:
+            raise ValueError(f"a {self.kind} group needs a positive length")
 
 
 class PagePool:
@@ -106,7 +107,7 @@ class CacheManager:
         if len(groups) != len(pages_per_group):
             raise ValueError("one page count per group is needed")
         self.groups = list(groups)
-        self._any_window = any(g.kind == "window" for g in self.groups)
+        self._any_window = any(g.kind != "full" for g in self.groups)  # some group gives pages back as a request grows
         self.page_size = page_size
         self.pools = [PagePool(n) for n in pages_per_group]
         self.num_slots = num_slots
@@ -150,9 +151,12 @@ class CacheManager:
     def _first_needed_page(self, g: int, start: int) -> int:
         """Index of the first page a query at position `start` (or later) can still read."""
         spec = self.groups[g]
-        if spec.kind != "window":
+        if spec.kind == "window":
+            oldest_key = max(0, start - spec.window + 1)
+        elif spec.kind == "chunk":
+            oldest_key = start // spec.window * spec.window  # the first position of the query's own block
+        else:
             return 0
-        oldest_key = max(0, start - spec.window + 1)
         return oldest_key // self.page_size
 
     def _plan(self, rc: RequestCache, start: int, new_len: int) -> list[tuple[int, int]]:

@@ -2,9 +2,13 @@
 // and the yardstick of the tensor-core kernels.
 //
 // For the query of token t (sequence b = seq_index[t], absolute position p = positions[t],
-// head g): keys lo..p of the same sequence from KV head g / (nq / nkv), where lo = 0 or
-// p - window + 1 for a sliding layer; s = (q . k) * scale; softmax over the keys;
-// o = sum p * v.  Scores, running max and sum, and the output accumulate in float32
+// head g): keys lo..p of the same sequence from KV head g / (nq / nkv), where lo = 0, or
+// p - window + 1 for a sliding layer, or the first position of p's block for a layer whose
+// queries see only their own block of `chunk` positions (blocks count from position 0 of the
+// sequence; the larger bound holds where a layer has both); s = (q . k) * scale; softmax over
+// the keys; o = sum p * v.  With `has_sink` the softmax's denominator also holds exp(sink_score):
+// a key that every query sees, whose score is fixed and which has no value.  Scores, running
+// max and sum, and the output accumulate in float32
 // (engine/nn/sdpa.py:56,85-102 of the reference: scale head_dim^-0.5, causal, GQA by head
 // ratio, keys and values read through the block table).  Key j of sequence b lives at
 // slot block_table[b][j / page] * page + j % page.
@@ -23,7 +27,7 @@ __global__ void attention_paged_simple_kernel(
     const TA* __restrict__ q, const TA* __restrict__ kcache, const TA* __restrict__ vcache,
     TA* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_index,
     const int* __restrict__ block_table, int max_blocks, int page, int T, int nq, int nkv, int d,
-    float scale, int window) {
+    float scale, int window, int chunk, int has_sink, float sink_score) {
   ts_pdl_prologue();
   __shared__ float qs[ATS_WARPS][ATS_MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -39,7 +43,8 @@ __global__ void attention_paged_simple_kernel(
     return;
   }
   const int p = positions[t];
-  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, p / chunk * chunk);
   const int* table = block_table + (size_t)b * max_blocks;
 
   const TA* qrow = q + ((size_t)t * nq + g) * d;
@@ -82,6 +87,13 @@ __global__ void attention_paged_simple_kernel(
     }
     m = m_new;
   }
+  if (has_sink) {  // the sink joins the denominator only: the sums of values shrink with it
+    const float m_new = fmaxf(m, sink_score);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(sink_score - m_new);
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) acc[i] *= corr;
+  }
   TA* orow = out + ((size_t)t * nq + g) * d;
   const float inv = 1.f / l;
 #pragma unroll
@@ -95,7 +107,8 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
                                         int act_dtype, void* out, const int* positions,
                                         const int* seq_index, const int* block_table,
                                         int max_blocks, int page, int T, int nq, int nkv, int d,
-                                        float scale, int window, void* stream) {
+                                        float scale, int window, int chunk, int has_sink, float sink_score,
+                                        void* stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || page <= 0 || max_blocks <= 0)
     return TS_ERR_BAD_ARGUMENT;
@@ -106,12 +119,12 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(attention_paged_simple_kernel<float>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const float*)q, (const float*)kcache, (const float*)vcache, (float*)out, positions,
-        seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window);
+        seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window, chunk, has_sink, sink_score);
   else if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(attention_paged_simple_kernel<__nv_bfloat16>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
         (__nv_bfloat16*)out, positions, seq_index, block_table, max_blocks, page, T, nq, nkv, d,
-        scale, window);
+        scale, window, chunk, has_sink, sink_score);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

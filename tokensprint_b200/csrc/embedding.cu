@@ -1,10 +1,11 @@
-// Token embedding: hidden[t, :] = table[ids[t], :], widened to the float32 residual stream.
+// Token embedding: hidden[t, :] = table[ids[t], :] * scale, widened to the float32 residual stream
+// (scale: a model's constant multiplier on its embedding rows, 1 for most).
 // (engine/model.py:65 of the reference: `seqs = self.embedding(seqs)`.)
 #include "common.cuh"
 
 template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ hidden, const TW* __restrict__ table,
-                                    const int* __restrict__ ids, int H, int V) {
+                                    const int* __restrict__ ids, int H, int V, float scale) {
   ts_pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -15,11 +16,11 @@ __global__ void embed_gather_kernel(float* __restrict__ hidden, const TW* __rest
     return;
   }
   const TW* src = table + (size_t)id * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ts_to_float(src[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ts_to_float(src[i]) * scale;
 }
 
 __global__ void embed_gather_bf16x8_kernel(float* __restrict__ hidden, const __nv_bfloat16* __restrict__ table,
-                                           const int* __restrict__ ids, int H, int V) {
+                                           const int* __restrict__ ids, int H, int V, float scale) {
   ts_pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -33,8 +34,8 @@ __global__ void embed_gather_bf16x8_kernel(float* __restrict__ hidden, const __n
       const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
       const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
       const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
-      a = make_float4(f0.x, f0.y, f1.x, f1.y);
-      b = make_float4(f2.x, f2.y, f3.x, f3.y);
+      a = make_float4(f0.x * scale, f0.y * scale, f1.x * scale, f1.y * scale);
+      b = make_float4(f2.x * scale, f2.y * scale, f3.x * scale, f3.y * scale);
     } else {
       const float nan = __int_as_float(0x7fc00000);
       a = b = make_float4(nan, nan, nan, nan);
@@ -45,17 +46,17 @@ __global__ void embed_gather_bf16x8_kernel(float* __restrict__ hidden, const __n
 }
 
 TS_EXPORT int ts_embed_gather(float* hidden, const void* table, int table_dtype, const int* ids,
-                              int T, int H, int V, void* stream) {
+                              int T, int H, int V, float scale, void* stream) {
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) return TS_ERR_BAD_ARGUMENT;
   int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
   if (table_dtype == TS_DTYPE_F32)
-    return ts_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, s, hidden, (const float*)table, ids, H, V);
+    return ts_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, s, hidden, (const float*)table, ids, H, V, scale);
   else if (table_dtype == TS_DTYPE_BF16 && H % 8 == 0 && ((uintptr_t)hidden | (uintptr_t)table) % 16 == 0)
-    return ts_launch(embed_gather_bf16x8_kernel, dim3(T), dim3(min(1024, max(32, (H / 8 + 31) / 32 * 32))), 0, s, hidden, (const __nv_bfloat16*)table, ids, H, V);
+    return ts_launch(embed_gather_bf16x8_kernel, dim3(T), dim3(min(1024, max(32, (H / 8 + 31) / 32 * 32))), 0, s, hidden, (const __nv_bfloat16*)table, ids, H, V, scale);
   else if (table_dtype == TS_DTYPE_BF16)
-    return ts_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, hidden, (const __nv_bfloat16*)table, ids, H, V);
+    return ts_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, hidden, (const __nv_bfloat16*)table, ids, H, V, scale);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

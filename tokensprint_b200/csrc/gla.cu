@@ -1,0 +1,191 @@
+// Gated linear attention: a recurrence with one decay per key channel, its state per request in
+// float32, for prompt portions and single decoded tokens alike.
+//
+// Per head, with q, k, decay of d entries and v of e entries per token, and a state S [d, e]:
+//   decay_t = sigmoid(z_t + bias)^(1/tau) = exp(logsigmoid(z_t + bias) / tau)
+//   S_t = diag(decay_t) S_(t-1) + k_t v_t^T          row c of S belongs to key channel c
+//   o_t = S_t^T (q_t * q_scale)
+// then  out_t = o_t * rsqrt(mean_e(o_t^2) + eps) * w_norm * silu(g_t)   per head (gla_norm_gate).
+//
+// gla_scan: one CTA per (sequence, head, block of value columns).  A thread owns one value column
+// and d / R consecutive key channels of it in registers (R lanes of a warp share a column and add
+// their partial outputs by shuffles).  The CTA walks its sequence's tokens of the step in order,
+// GLA_TB at a time: q, k, the decay (worked out here, in float32, from z) and v of those tokens are
+// staged in shared memory by all threads, then every thread runs the GLA_TB updates from there.
+// The state is read from the request's slot before the first token and written back after the
+// last, so a sequence may be cut anywhere, and a token's result depends on nothing but its own
+// sequence: the same sums in the same order whatever else is in the batch.
+// A sequence without tokens in this step (a padded lane of a fixed-size batch) touches nothing.
+#include "common.cuh"
+
+#define GLA_TB 16        // tokens staged at a time, at most (fewer where d is so large that 16 do not fit 48 KB)
+#define GLA_MAX_KP 32    // key channels per thread, at most
+#define GLA_THREADS 128
+
+__device__ __forceinline__ float gla_log_sigmoid(float z) {
+  // log(1 / (1 + exp(-z))) without overflow on either side
+  return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+}
+
+template <typename TA, int KP>
+__global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
+    const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const TA* __restrict__ z,
+    long long ld_z, const float* __restrict__ bias, float inv_tau, float q_scale, float* __restrict__ state,
+    const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H, int d, int e, int R,
+    int cols_per_cta, int tb) {
+  ts_pdl_prologue();
+  extern __shared__ float sm[];
+  // staged per token: q, k, decay [dp] each, v [cols]
+  const int dp = R * KP;  // d padded to the channels the threads cover
+  float* sq = sm;
+  float* sk = sq + tb * dp;
+  float* sa = sk + tb * dp;
+  float* sv = sa + tb * dp;  // [tb][cols_per_cta]
+  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_cta;
+  const int t_begin = cu_seqlens[b], t_end = cu_seqlens[b + 1];
+  if (t_end <= t_begin) return;
+  const int r = threadIdx.x % R, cj = threadIdx.x / R;  // lanes of one column sit side by side
+  const int col = col0 + cj;
+  const bool has_col = cj < cols_per_cta && col < e;
+  const int c0 = r * KP;
+  float* S = state + (((size_t)state_slots[b] * H + h) * d) * e;
+  float s_reg[KP];
+#pragma unroll
+  for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? S[(size_t)(c0 + i) * e + col] : 0.f;
+
+  const size_t qk_off = (size_t)h * d, v_off = (size_t)h * e + col0;
+  for (int t0 = t_begin; t0 < t_end; t0 += tb) {
+    const int nt = min(tb, t_end - t0);
+    __syncthreads();  // the round before has been read
+    for (int i = threadIdx.x; i < nt * dp; i += GLA_THREADS) {
+      const int tt = i / dp, c = i - tt * dp;
+      float qv = 0.f, kv = 0.f, av = 1.f;
+      if (c < d) {
+        const size_t at = (size_t)(t0 + tt) * ld_qkv + qk_off + c;
+        qv = ts_to_float(q[at]) * q_scale;
+        kv = ts_to_float(k[at]);
+        const float zz = ts_to_float(z[(size_t)(t0 + tt) * ld_z + qk_off + c]) + (bias ? bias[qk_off + c] : 0.f);
+        av = expf(gla_log_sigmoid(zz) * inv_tau);
+      }
+      sq[i] = qv;
+      sk[i] = kv;
+      sa[i] = av;
+    }
+    for (int i = threadIdx.x; i < nt * cols_per_cta; i += GLA_THREADS) {
+      const int tt = i / cols_per_cta, c = i - tt * cols_per_cta;
+      sv[i] = (col0 + c < e) ? ts_to_float(v[(size_t)(t0 + tt) * ld_qkv + v_off + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vv = cj < cols_per_cta ? sv[tt * cols_per_cta + cj] : 0.f;
+      const float* pq = sq + tt * dp + c0;
+      const float* pk = sk + tt * dp + c0;
+      const float* pa = sa + tt * dp + c0;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < KP; ++i) {
+        s_reg[i] = fmaf(pa[i], s_reg[i], pk[i] * vv);
+        acc = fmaf(s_reg[i], pq[i], acc);
+      }
+      for (int w = 1; w < R; w <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+      if (r == 0 && has_col) o[((size_t)(t0 + tt) * H + h) * e + col] = acc;
+    }
+  }
+  if (has_col) {
+#pragma unroll
+    for (int i = 0; i < KP; ++i)
+      if (c0 + i < d) S[(size_t)(c0 + i) * e + col] = s_reg[i];
+  }
+}
+
+template <typename TA, int KP>
+static int launch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, const float* bias,
+                           float inv_tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H,
+                           int d, int e, int R, cudaStream_t s) {
+  const int cols = GLA_THREADS / R;
+  const size_t per_token = (size_t)(3 * R * KP + cols) * sizeof(float);
+  const int tb = (int)min((size_t)GLA_TB, (size_t)(48 * 1024) / per_token);
+  if (tb < 1) return TS_ERR_UNSUPPORTED_SIZE;
+  const size_t smem = tb * per_token;
+  const dim3 grid(B, H, (e + cols - 1) / cols);
+  if (grid.y > 65535 || grid.z > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  return ts_launch(gla_scan_kernel<TA, KP>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, (const TA*)z,
+                   ld_z, bias, inv_tau, q_scale, state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb);
+}
+
+template <typename TA>
+static int dispatch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, const float* bias,
+                             float inv_tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H,
+                             int d, int e, cudaStream_t s) {
+  // R lanes per column, a power of two, so that a thread holds at most GLA_MAX_KP channels
+  int R = 1;
+  while (R < 32 && (d + R - 1) / R > GLA_MAX_KP) R <<= 1;
+  // fewer channels per thread where that fills the lanes better (decode: the state's bytes are the work)
+  while (R < 4 && (d + R - 1) / R > 8) R <<= 1;
+  const int kp = (d + R - 1) / R;
+  if (kp > GLA_MAX_KP) return TS_ERR_UNSUPPORTED_SIZE;  // d > 1024
+#define GLA_CASE(KP) \
+  if (kp <= KP) return launch_gla_scan<TA, KP>(q, k, v, ld_qkv, z, ld_z, bias, inv_tau, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, s)
+  GLA_CASE(4);
+  GLA_CASE(8);
+  GLA_CASE(12);
+  GLA_CASE(16);
+  GLA_CASE(24);
+  GLA_CASE(32);
+#undef GLA_CASE
+  return TS_ERR_UNSUPPORTED_SIZE;
+}
+
+// q, k [T, H*d] and v [T, H*e] are views with the common row stride ld_qkv (columns of one product's
+// result); z [T, H*d] with row stride ld_z; bias [H*d] float32; state [slots, H, d, e] float32;
+// o [T, H*e] float32.
+TS_EXPORT int ts_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, int act_dtype,
+                          const float* bias, float tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens,
+                          float* o, int B, int H, int d, int e, void* stream) {
+  if (B <= 0) return 0;
+  if (H <= 0 || d <= 0 || e <= 0 || !(tau > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32)
+    return dispatch_gla_scan<float>(q, k, v, ld_qkv, z, ld_z, bias, 1.f / tau, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, s);
+  if (act_dtype == TS_DTYPE_BF16)
+    return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, z, ld_z, bias, 1.f / tau, q_scale, state, state_slots, cu_seqlens, o, B, H, d,
+                                            e, s);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+// out[t, h, :] = o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * w * silu(g[t, h, :]); one warp per (token, head).
+template <typename TA>
+__global__ void gla_norm_gate_kernel(const float* __restrict__ o, const TA* __restrict__ g, long long ld_g, const float* __restrict__ w,
+                                     TA* __restrict__ out, int T, int H, int e, float eps) {
+  ts_pdl_prologue();
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= (long long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+  const float* row = o + ((size_t)t * H + h) * e;
+  float ss = 0.f;
+  for (int i = lane; i < e; i += 32) ss += row[i] * row[i];
+  ss = ts_warp_sum(ss);
+  const float rstd = 1.f / sqrtf(ss / (float)e + eps);
+  const TA* grow = g + (size_t)t * ld_g + (size_t)h * e;
+  TA* orow = out + ((size_t)t * H + h) * e;
+  for (int i = lane; i < e; i += 32) {
+    const float gate = ts_to_float(grow[i]);
+    orow[i] = ts_from_float<TA>(row[i] * rstd * w[i] * (gate / (1.f + expf(-gate))));
+  }
+}
+
+TS_EXPORT int ts_gla_norm_gate(const float* o, const void* g, long long ld_g, int act_dtype, const float* w, void* out, int T, int H, int e,
+                               float eps, void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || e <= 0) return TS_ERR_BAD_ARGUMENT;
+  const long long items = (long long)T * H;
+  const unsigned blocks = (unsigned)((items + 3) / 4);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32)
+    return ts_launch(gla_norm_gate_kernel<float>, dim3(blocks), dim3(128), 0, s, o, (const float*)g, ld_g, w, (float*)out, T, H, e, eps);
+  if (act_dtype == TS_DTYPE_BF16)
+    return ts_launch(gla_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, s, o, (const __nv_bfloat16*)g, ld_g, w,
+                     (__nv_bfloat16*)out, T, H, e, eps);
+  return TS_ERR_BAD_ARGUMENT;
+}

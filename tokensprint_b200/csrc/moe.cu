@@ -1,15 +1,17 @@
 // A feed-forward of routed experts, for any sizes and both element types, without a trip to the
 // host: every grid is sized from the step's token count alone.
 //
-//   router_topk : per token, from float32 router logits: score = sigmoid(logit), the `top` largest
-//                 scores (the lower index wins a tie) with their experts; the scores are handed on
-//                 as they are, or divided by their sum (`renormalize`).
+//   router_topk : per token, from float32 router logits (+ a bias per expert, if given): the `top`
+//                 largest logits (the lower index wins a tie) with their experts; their weights are
+//                 sigmoid(logit), handed on as they are or divided by their sum (`renormalize`), or
+//                 the softmax over the chosen logits alone (`score_mode`).
 //   moe_plan    : the (token, choice) pairs sorted by expert: offsets[e] .. offsets[e+1] are expert
 //                 e's places in `order` (pair indices), tile_offsets[e] its first row tile of
 //                 `tile_rows` places (64 for the kernels here, more for the tensor-core ones).
 //   moe_gate_up : for the pairs of each expert, rows x[token] * weight(pair) times the expert's gate
-//                 and up matrices, then a = min(g, limit), b = clamp(u, -limit, limit),
-//                 act = a * sigmoid(alpha a) * (b + 1)           -> act[place, I]
+//                 and up matrices, then the gated activation (`act_mode`): with a = min(g, limit),
+//                 b = clamp(u, -limit, limit), a * sigmoid(alpha a) * (b + 1); or silu(g) * u
+//                                                                  -> act[place, I]
 //   moe_down    : act[place] times the expert's down matrix       -> pair_out[pair, N]
 //   moe_combine : out[t] = sum over the token's pairs (each times its weight, if weights are given)
 //                 (+ shared[t]), summed in float32 in the order of the choices.
@@ -18,21 +20,18 @@
 // pair's result does not depend on its place inside its expert's rows, so the order in which the
 // plan happens to list an expert's pairs changes nothing.
 #include "common.cuh"
+#include "moe_act.cuh"
 
 #define MOE_BM 64
 #define MOE_BN 64
 #define MOE_BK 16
 #define MOE_MAX_EXPERTS 4096
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, int T, int E, int top, int renormalize, int* __restrict__ ids,
-                                   float* __restrict__ weights) {
-  ts_pdl_prologue();
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= T) return;
-  const float* z = logits + (size_t)warp * E;
-  int* my_ids = ids + (size_t)warp * top;
-  float* my_w = weights + (size_t)warp * top;
-  float total = 0.f;
+
+// The choice of one token by one warp: logits z [E] (shared or global memory), the bias already in.
+__device__ __forceinline__ void router_choose(const float* z, int E, int top, int renormalize, int score_mode, int* my_ids, float* my_w,
+                                              int lane) {
+  float total = 0.f, first = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -54,7 +53,8 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int T, int 
         best_e = oe;
       }
     }
-    const float score = 1.f / (1.f + expf(-best));
+    if (k == 0) first = best;  // the largest logit: the softmax's reference point
+    const float score = score_mode == ROUTER_SCORE_SOFTMAX_CHOSEN ? expf(best - first) : 1.f / (1.f + expf(-best));
     total += score;
     if (lane == 0) {
       my_ids[k] = best_e < E ? best_e : 0;
@@ -62,14 +62,30 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int T, int 
     }
     __syncwarp();
   }
-  if (renormalize && lane == 0)
+  if ((renormalize || score_mode == ROUTER_SCORE_SOFTMAX_CHOSEN) && lane == 0)
     for (int k = 0; k < top; ++k) my_w[k] /= total;
 }
 
-TS_EXPORT int ts_router_topk(const float* logits, int T, int E, int top, int renormalize, int* ids, float* weights, void* stream) {
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int top, int renormalize,
+                                   int score_mode, int* __restrict__ ids, float* __restrict__ weights) {
+  ts_pdl_prologue();
+  extern __shared__ float zs[];  // [4][E]: a token's logits with the bias added
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * (blockDim.x >> 5) + w;
+  if (warp >= T) return;
+  float* z = zs + (size_t)w * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)warp * E + e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  router_choose(z, E, top, renormalize, score_mode, ids + (size_t)warp * top, weights + (size_t)warp * top, lane);
+}
+
+TS_EXPORT int ts_router_topk(const float* logits, const float* bias, int T, int E, int top, int renormalize, int score_mode, int* ids,
+                             float* weights, void* stream) {
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
-  return ts_launch(router_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, T, E, top, renormalize, ids, weights);
+  if ((size_t)4 * E * sizeof(float) > 48 * 1024) return TS_ERR_UNSUPPORTED_SIZE;
+  return ts_launch(router_topk_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream, logits, bias, T, E,
+                   top, renormalize, score_mode, ids, weights);
 }
 
 // One block: counts per expert, their prefix sums, then every pair takes the next place of its expert.
@@ -128,7 +144,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TA* __restrict__
                                                           const int* __restrict__ order, const int* __restrict__ offsets,
                                                           const int* __restrict__ tile_offsets, const TA* __restrict__ gate,
                                                           const TA* __restrict__ up, TA* __restrict__ act, int E, int K, int I, int top,
-                                                          float limit, float alpha) {
+                                                          float limit, float alpha, int act_mode) {
   ts_pdl_prologue();
   __shared__ float As[MOE_BK][MOE_BM + 1];
   __shared__ float Gs[MOE_BK][MOE_BN + 1];
@@ -191,9 +207,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TA* __restrict__
       if (gn >= I) continue;
       // the sums are rounded to the element type first, as a product stored to memory would be
       const float gv = ts_to_float(ts_from_float<TA>(accg[i][j])), uv = ts_to_float(ts_from_float<TA>(accu[i][j]));
-      const float a = fminf(gv, limit);
-      const float b = fminf(fmaxf(uv, -limit), limit);
-      act[(size_t)place * I + gn] = ts_from_float<TA>(a / (1.f + expf(-alpha * a)) * (b + 1.f));
+      act[(size_t)place * I + gn] = ts_from_float<TA>(moe_gated_activation(act_mode, gv, uv, limit, alpha));
     }
   }
 }
@@ -250,7 +264,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const TA* __restrict__ ac
 
 TS_EXPORT int ts_moe_gate_up(const void* x, int act_dtype, const float* pair_weight, const int* order, const int* offsets,
                              const int* tile_offsets, const void* gate, const void* up, void* act, int P, int E, int K, int I, int top,
-                             float limit, float alpha, void* stream) {
+                             float limit, float alpha, int act_mode, void* stream) {
   if (P <= 0) return 0;
   if (E <= 0 || K <= 0 || I <= 0 || top <= 0) return TS_ERR_BAD_ARGUMENT;
   const dim3 grid((I + MOE_BN - 1) / MOE_BN, (P + MOE_BM - 1) / MOE_BM + E);
@@ -258,10 +272,10 @@ TS_EXPORT int ts_moe_gate_up(const void* x, int act_dtype, const float* pair_wei
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(moe_gate_up_kernel<float>, grid, dim3(256), 0, s, (const float*)x, pair_weight, order, offsets, tile_offsets,
-                     (const float*)gate, (const float*)up, (float*)act, E, K, I, top, limit, alpha);
+                     (const float*)gate, (const float*)up, (float*)act, E, K, I, top, limit, alpha, act_mode);
   if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x, pair_weight, order, offsets,
-                     tile_offsets, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)act, E, K, I, top, limit, alpha);
+                     tile_offsets, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)act, E, K, I, top, limit, alpha, act_mode);
   return TS_ERR_BAD_ARGUMENT;
 }
 
@@ -320,9 +334,9 @@ TS_EXPORT int ts_moe_combine(const void* pair_out, const void* shared, void* out
 #define ROUTER_MAX_TOKENS 4
 
 template <typename TX>
-__global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, const float* __restrict__ router, int T, int W, int E,
-                                                     int top, int renormalize, int rt, int* __restrict__ ids,
-                                                     float* __restrict__ weights) {
+__global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, const float* __restrict__ router,
+                                                     const float* __restrict__ bias, int T, int W, int E, int top, int renormalize,
+                                                     int score_mode, int rt, int* __restrict__ ids, float* __restrict__ weights) {
   ts_pdl_prologue();
   extern __shared__ float rs[];
   float* xs = rs;                    // [rt][W]
@@ -361,50 +375,17 @@ __global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, c
 #pragma unroll
     for (int j = 0; j < ROUTER_MAX_TOKENS; ++j) {
       const float v = ts_warp_sum(acc[j]);
-      if (lane == 0 && j < nt) logits[(size_t)j * E + e] = v;
+      if (lane == 0 && j < nt) logits[(size_t)j * E + e] = v + (bias ? bias[e] : 0.f);
     }
   }
   __syncthreads();
   if (warp >= nt) return;
-  const float* z = logits + (size_t)warp * E;
-  int* my_ids = ids + (size_t)(t0 + warp) * top;
-  float* my_w = weights + (size_t)(t0 + warp) * top;
-  float total = 0.f;
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int best_e = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      bool taken = false;
-      for (int j = 0; j < k; ++j) taken |= (my_ids[j] == e);
-      const float v = z[e];
-      if (!taken && (v > best || (v == best && e < best_e))) {
-        best = v;
-        best_e = e;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ov > best || (ov == best && oe < best_e)) {
-        best = ov;
-        best_e = oe;
-      }
-    }
-    const float score = 1.f / (1.f + expf(-best));
-    total += score;
-    if (lane == 0) {
-      my_ids[k] = best_e < E ? best_e : 0;
-      my_w[k] = score;
-    }
-    __syncwarp();
-  }
-  if (renormalize && lane == 0)
-    for (int k = 0; k < top; ++k) my_w[k] /= total;
+  router_choose(logits + (size_t)warp * E, E, top, renormalize, score_mode, ids + (size_t)(t0 + warp) * top,
+                weights + (size_t)(t0 + warp) * top, lane);
 }
 
-TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, int T, int W, int E, int top, int renormalize, int* ids,
-                        float* weights, void* stream) {
+TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, const float* bias, int T, int W, int E, int top, int renormalize,
+                        int score_mode, int* ids, float* weights, void* stream) {
   if (T <= 0) return 0;
   if (W <= 0 || E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
   // tokens per CTA: four where there are CTAs enough for every SM several times over (a router row is
@@ -422,7 +403,7 @@ TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, int T, 
       if (e != cudaSuccess) return (int)e;
       set32 = 227 * 1024;
     }
-    return ts_launch(router_kernel<float>, grid, dim3(256), smem, s, (const float*)x, router, T, W, E, top, renormalize, rt, ids, weights);
+    return ts_launch(router_kernel<float>, grid, dim3(256), smem, s, (const float*)x, router, bias, T, W, E, top, renormalize, score_mode, rt, ids, weights);
   }
   if (x_dtype == TS_DTYPE_BF16) {
     static size_t set16 = 0;
@@ -431,8 +412,8 @@ TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, int T, 
       if (e != cudaSuccess) return (int)e;
       set16 = 227 * 1024;
     }
-    return ts_launch(router_kernel<__nv_bfloat16>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x, router, T, W, E, top, renormalize, rt,
-                     ids, weights);
+    return ts_launch(router_kernel<__nv_bfloat16>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x, router, bias, T, W, E, top, renormalize,
+                     score_mode, rt, ids, weights);
   }
   return TS_ERR_BAD_ARGUMENT;
 }

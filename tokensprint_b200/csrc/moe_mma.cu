@@ -10,6 +10,7 @@
 // the float32 sums, not the rounded input: (w x) . g = w (x . g) without a second rounding of x.
 // Every output element is one chain of sums over k in a fixed order, whatever rows share the tile.
 #include "common.cuh"
+#include "moe_act.cuh"
 
 namespace {
 
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat
                                                                const int* __restrict__ order, const int* __restrict__ offsets,
                                                                const int* __restrict__ tile_offsets, const __nv_bfloat16* __restrict__ B0,
                                                                const __nv_bfloat16* __restrict__ B1, __nv_bfloat16* __restrict__ out, int E,
-                                                               int K, int NOUT, int top, float limit, float alpha) {
+                                                               int K, int NOUT, int top, float limit, float alpha, int act_mode) {
   constexpr int BM = 16 * MT * WM, THREADS = 32 * WM * WN, CW = NB / WN, HALF = CW / 2, NT = CW / 8;
   constexpr size_t STAGE_ELEMS = (size_t)(BM + NB) * KS;
   ts_pdl_prologue();
@@ -157,8 +158,7 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat
             // the sums are rounded to bfloat16 first, as a product stored to memory would be
             const float gv = __bfloat162float(__float2bfloat16_rn(w * acc[m][nb][2 * r + c]));
             const float uv = __bfloat162float(__float2bfloat16_rn(w * acc[m][nb + NT / 2][2 * r + c]));
-            const float a = fminf(gv, limit), b = fminf(fmaxf(uv, -limit), limit);
-            y[c] = a / (1.f + expf(-alpha * a)) * (b + 1.f);
+            y[c] = moe_gated_activation(act_mode, gv, uv, limit, alpha);
           }
           if (n + 1 < NOUT && (NOUT & 1) == 0) {
             *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(y[0], y[1]);
@@ -190,7 +190,7 @@ constexpr int ROWS_MANY = 128, ROWS_FEW = 16;
 
 template <bool GATE_UP, int WM, int WN, int MT, int STAGES>
 int launch(const void* A, const float* pair_weight, const int* order, const int* offsets, const int* tile_offsets, const void* B0,
-           const void* B1, void* out, int P, int E, int K, int NOUT, int top, float limit, float alpha, cudaStream_t s) {
+           const void* B1, void* out, int P, int E, int K, int NOUT, int top, float limit, float alpha, int act_mode, cudaStream_t s) {
   constexpr int BM = 16 * MT * WM;
   constexpr size_t SMEM_BYTES = (size_t)STAGES * (BM + NB) * KS * 2;
   static bool configured = false;
@@ -204,7 +204,7 @@ int launch(const void* A, const float* pair_weight, const int* order, const int*
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
   return ts_launch(moe_mma_kernel<GATE_UP, WM, WN, MT, STAGES>, grid, dim3(32 * WM * WN), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight,
                    order, offsets, tile_offsets, (const __nv_bfloat16*)B0, (const __nv_bfloat16*)B1, (__nv_bfloat16*)out, E, K, NOUT, top,
-                   limit, alpha);
+                   limit, alpha, act_mode);
 }
 
 }  // namespace
@@ -216,13 +216,13 @@ TS_EXPORT int ts_moe_mma_row_tile(int few_rows) { return few_rows ? ROWS_FEW : R
 // tile_rows: the row tile the plan was made for (one of the two above).
 TS_EXPORT int ts_moe_gate_up_mma(const void* x, const float* pair_weight, const int* order, const int* offsets, const int* tile_offsets,
                                  const void* gate, const void* up, void* act, int P, int E, int K, int I, int top, float limit, float alpha,
-                                 int tile_rows, void* stream) {
+                                 int act_mode, int tile_rows, void* stream) {
   if (P <= 0) return 0;
   if (E <= 0 || K <= 0 || I <= 0 || top <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (K % 8 || (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)up) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
   if (tile_rows == ROWS_MANY)
-    return launch<true, 2, 4, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
-  return launch<true, 1, 4, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, (cudaStream_t)stream);
+    return launch<true, 2, 4, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
+  return launch<true, 1, 4, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
 }
 
 TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offsets, const int* tile_offsets, const void* down,
@@ -231,6 +231,6 @@ TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offs
   if (E <= 0 || I <= 0 || N <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (I % 8 || (((uintptr_t)act | (uintptr_t)down) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
   if (tile_rows == ROWS_MANY)
-    return launch<false, 2, 4, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
-  return launch<false, 1, 4, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, (cudaStream_t)stream);
+    return launch<false, 2, 4, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, 0, (cudaStream_t)stream);
+  return launch<false, 1, 4, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, 0, (cudaStream_t)stream);
 }

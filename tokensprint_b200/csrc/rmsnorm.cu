@@ -272,3 +272,85 @@ TS_EXPORT int ts_round_rows(const void* in, int in_dtype, void* out, int out_dty
     return ts_launch(round_rows_kernel<float, float>, dim3(blocks), dim3(256), 0, s, (const float*)in, (float*)out, (size_t)n);
   return TS_ERR_BAD_ARGUMENT;
 }
+
+// A sublayer between two norms, with a learned scale per channel on its way back into the stream:
+//   hidden[row] += branch[row] * rsqrt(mean(branch[row]^2) + eps) * weight * scale      (scale may be absent)
+// and, if the next norm's weight is given, that norm on the new row in the same pass:
+//   out[row] = hidden[row] * rsqrt(mean(hidden[row]^2) + next_eps) * next_weight
+// All sums and the stream in float32; `out` in the compute type.  One CTA per row; the row stays in
+// registers between the two sums of squares where it is short enough, else it is read again.
+#define BN_KEEP 8  // elements a thread keeps between the passes
+template <typename TB, typename TO>
+__global__ void branch_norm_add_kernel(const TB* __restrict__ branch, const float* __restrict__ weight, const float* __restrict__ scale,
+                                       float* __restrict__ hidden, const float* __restrict__ next_weight, TO* __restrict__ out, int H,
+                                       float eps, float next_eps) {
+  ts_pdl_prologue();
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const TB* b = branch + (size_t)row * H;
+  float* h = hidden + (size_t)row * H;
+  const bool keep = H <= BN_KEEP * (int)blockDim.x;
+  float kept[BN_KEEP];
+  float ss = 0.f;
+  for (int i = threadIdx.x, n = 0; i < H; i += blockDim.x, ++n) {
+    const float v = ts_to_float(b[i]);
+    if (keep && n < BN_KEEP) kept[n] = v;
+    ss += v * v;
+  }
+  ss = ts_block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)H + eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x, n = 0; i < H; i += blockDim.x, ++n) {
+    const float bv = (keep && n < BN_KEEP) ? kept[n] : ts_to_float(b[i]);
+    float add = bv * rstd * weight[i];
+    if (scale) add *= scale[i];
+    const float v = h[i] + add;
+    h[i] = v;
+    if (keep && n < BN_KEEP) kept[n] = v;
+    ss2 += v * v;
+  }
+  if (next_weight == nullptr) return;
+  ss2 = ts_block_sum(ss2, scratch);
+  const float rstd2 = 1.f / sqrtf(ss2 / (float)H + next_eps);
+  for (int i = threadIdx.x, n = 0; i < H; i += blockDim.x, ++n) {
+    const float v = (keep && n < BN_KEEP) ? kept[n] : h[i];
+    out[(size_t)row * H + i] = ts_from_float<TO>(v * rstd2 * next_weight[i]);
+  }
+}
+
+TS_EXPORT int ts_branch_norm_add(const void* branch, int branch_dtype, const float* weight, const float* scale, float* hidden,
+                                 const float* next_weight, void* out, int out_dtype, int rows, int H, float eps, float next_eps,
+                                 void* stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || (next_weight != nullptr && out == nullptr)) return TS_ERR_BAD_ARGUMENT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
+  if (next_weight == nullptr) out_dtype = branch_dtype;
+  if (branch_dtype == TS_DTYPE_F32 && out_dtype == TS_DTYPE_F32)
+    return ts_launch(branch_norm_add_kernel<float, float>, dim3(rows), dim3(threads), 0, s, (const float*)branch, weight, scale, hidden,
+                     next_weight, (float*)out, H, eps, next_eps);
+  if (branch_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_BF16)
+    return ts_launch(branch_norm_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (const __nv_bfloat16*)branch,
+                     weight, scale, hidden, next_weight, (__nv_bfloat16*)out, H, eps, next_eps);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+// hidden[row] += rows[row] (if given) + vector (if given), float32: what a model adds to the stream
+// between two runs of layers (the embedding rows once more, a learned vector per pass).
+__global__ void stream_add_kernel(float* __restrict__ hidden, const float* __restrict__ rows, const float* __restrict__ vector, int H,
+                                  size_t n) {
+  ts_pdl_prologue();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = hidden[i];
+  if (rows) v += rows[i];
+  if (vector) v += vector[i % H];
+  hidden[i] = v;
+}
+
+TS_EXPORT int ts_stream_add(float* hidden, const float* rows, const float* vector, int T, int H, void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0) return TS_ERR_BAD_ARGUMENT;
+  const size_t n = (size_t)T * H;
+  return ts_launch(stream_add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, hidden, rows, vector, H, n);
+}

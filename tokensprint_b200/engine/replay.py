@@ -29,7 +29,7 @@ from tokensprint_b200.models.api import load_model
 
 # Defaults of the command line; every one of them is an option.
 PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 4  # state slots: no more requests are live at a time
 TOKEN_ROUNDING = 64  # --max-tokens counts each live request rounded up to a multiple of this
 
 

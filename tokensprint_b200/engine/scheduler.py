@@ -60,11 +60,12 @@ class Scheduler:
         cm = self.cache_manager
         # The most pages the request holds at once: all of them in a group that keeps every key;
         # in a window group all of them too when the prompt comes in one portion (pages are given
-        # back between steps only), else the window plus the largest portion.
+        # back between steps only), else the window plus the largest portion (a chunk group
+        # likewise: at most one block of positions before the portion's first token is held).
         for g, pool in enumerate(cm.pools):
             spec = cm.groups[g]
             tokens = len(seq) + 1
-            if spec.kind == "window" and self.enable_chunked:
+            if spec.kind in ("window", "chunk") and self.enable_chunked:
                 tokens = min(tokens, spec.window + self.max_num_batched_tokens + cm.page_size)
             need = -(-tokens // cm.page_size)
             if need > pool.num_pages:

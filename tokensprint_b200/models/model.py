@@ -10,7 +10,7 @@ import torch
 import tokensprint_b200.parts  # noqa: F401  (registers the built-in parts)
 from tokensprint_b200 import ops
 from tokensprint_b200.models.spec import ModelSpec
-from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, PreNormed, Rounded, StepContext, TensorSpec, build_part
+from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, Normed, PreNormed, Rounded, StepContext, TensorSpec, build_part
 from tokensprint_b200.parts.linear import folding_possible, linear_float32_out, linear_scaled
 from tokensprint_b200.weights.loader import LoadedTensors, WeightSource, check_tensors
 
@@ -40,7 +40,9 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, ctx)
         self.embedding_transform = None if spec.embedding_transform is None else build_part("transform", spec.embedding_transform, ctx)
         self.logits_transform = None if spec.logits_transform is None else build_part("transform", spec.logits_transform, ctx)
-        self._transforms = [t for t in (self.embedding_transform, self.logits_transform) if t is not None]
+        self.run_transforms = [build_part("transform", t, ctx) for t in spec.run_transforms]
+        self._transforms = [t for t in (self.embedding_transform, self.logits_transform, *self.run_transforms) if t is not None]
+        self._keeps_embedding = any(run.before is not None for run in spec.run_order)
         self.graph_safe = (all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
                            and all(t.graph_safe for t in self._transforms))
         self.embedding: Optional[torch.Tensor] = None
@@ -132,12 +134,14 @@ class Model:
         T = step.num_tokens
         step.shared.clear()  # what parts share lasts one run of the blocks (a step's description may be run again: warm-up, then capture)
         hidden = torch.empty((T, self.spec.hidden_size), device=self.device, dtype=torch.float32)
-        ops.embed_gather(hidden, self.embedding, step.token_ids)
+        ops.embed_gather(hidden, self.embedding, step.token_ids, self.spec.embedding_scale)
         if self.embedding_transform is not None:
             if self._embedding_cache is not None:
                 hidden = self.embedding_transform.forward(hidden, step, cache=caches[self._embedding_cache])
             else:
                 hidden = self.embedding_transform.forward(hidden, step)
+        # the embedding rows as they enter the first block, for transforms between runs that want them
+        embedding_rows = hidden.clone() if self._keeps_embedding else None
         pending = None
         order = self.spec.run_order
         # the final norm may be prepared by the last block when every row's logits are wanted
@@ -148,6 +152,16 @@ class Model:
             last = i + 1 == len(order)
             step.weight_after = self.head if last else self.blocks[order[i + 1].layer].first_weight()
             step.norm_after = (self.final_norm if fold_final else None) if last else self.blocks[order[i + 1].layer].entry_norm()
+            if not last and order[i + 1].before is not None:
+                step.norm_after = None  # the stream changes once more before the next block's norm reads it
+            if run.before is not None:
+                if isinstance(pending, torch.Tensor):  # the transform works on the complete stream
+                    ops.residual_add(hidden, pending)
+                pending = None
+                transform = self.run_transforms[run.before]
+                if not transform.reads_through_ops:
+                    ops.flush_gemm_chain()
+                hidden = transform.forward(hidden, step, embedding=embedding_rows)
             block = self.blocks[run.layer]
             if not block.reads_through_ops:
                 ops.flush_gemm_chain()
@@ -176,6 +190,10 @@ class Model:
     def _head_product(self, hidden: torch.Tensor, pending, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
         if isinstance(pending, Rounded):
             pending = None  # `hidden` is complete
+        if isinstance(pending, Normed):  # the final norm of every row, done by the last block's last kernel
+            if num_rows == hidden.shape[0]:
+                return linear_float32_out(pending.x, self.head)
+            pending = None  # `hidden` is complete: norm the wanted rows as usual
         if isinstance(pending, PreNormed):
             if num_rows == hidden.shape[0] and folding_possible(num_rows, self.dtype, self.head):
                 return linear_scaled(pending, self.head, float32_out=True)

@@ -17,11 +17,16 @@ class RunSpec:
     cache: id of the cache this run uses; None gives the run a fresh cache of its own.
     Two runs with the same id share it; the one with `writes_cache` fills it, the others
     read what it stored.
+    before: index into `ModelSpec.run_transforms` of a transform that works on the (complete)
+    residual stream right before this run's block: what a model adds to the stream between two
+    stretches of layers.  It is called as forward(hidden, step, embedding=rows), `rows` being the
+    embedding rows as they entered the first block (float32 [T, width]).
     """
 
     layer: int
     cache: Optional[int] = None
     writes_cache: bool = True
+    before: Optional[int] = None
 
 
 @dataclass
@@ -43,6 +48,10 @@ class ModelSpec:
     # (float32 [T, width]) and to the logits after the head (float32 [rows, vocab]).
     embedding_transform: Optional[PartSpec] = None
     logits_transform: Optional[PartSpec] = None
+    # A constant that multiplies the embedding rows as they are gathered.
+    embedding_scale: float = 1.0
+    # "transform" parts that runs of the run order name as their `before`.
+    run_transforms: list[PartSpec] = field(default_factory=list)
 
     def __post_init__(self) -> None:
         if not self.run_order:
@@ -50,6 +59,8 @@ class ModelSpec:
         for run in self.run_order:
             if not (0 <= run.layer < len(self.layers)):
                 raise ValueError(f"run order names layer {run.layer}, the model has {len(self.layers)}")
+            if run.before is not None and not (0 <= run.before < len(self.run_transforms)):
+                raise ValueError(f"run order names transform {run.before}, the model has {len(self.run_transforms)}")
 
     def tensor_specs(self) -> list[TensorSpec]:
         """Every tensor the model wants, each name once (built on a CPU context, no GPU needed)."""
@@ -70,7 +81,7 @@ class ModelSpec:
                 add(s)
         for s in build_part("norm", self.final_norm, ctx).tensor_specs():
             add(s)
-        for transform in (self.embedding_transform, self.logits_transform):
+        for transform in (self.embedding_transform, self.logits_transform, *self.run_transforms):
             if transform is not None:
                 for s in build_part("transform", transform, ctx).tensor_specs():
                     add(s)

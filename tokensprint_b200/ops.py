@@ -24,7 +24,7 @@ _c_float = ctypes.c_float
 _c_ll = ctypes.c_longlong
 
 _SIGNATURES = {
-    "ts_embed_gather": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_embed_gather": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "ts_feed_tokens": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "ts_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "ts_residual_add": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
@@ -35,7 +35,7 @@ _SIGNATURES = {
     ],
     "ts_attention_paged_simple": [
         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_float, _c_void_p,
     ],
     "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "ts_sgemm_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
@@ -51,15 +51,23 @@ _SIGNATURES = {
     "ts_gelu_tanh": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "ts_capped_glu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "ts_gelu_gate_rows": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_void_p],
-    "ts_router_topk": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
-    "ts_router": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "ts_router_topk": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "ts_router": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "ts_moe_gate_up_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                           _c_int, _c_int, _c_float, _c_float, _c_int, _c_void_p],
+                           _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_void_p],
     "ts_moe_down_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "ts_moe_gate_up": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                       _c_int, _c_int, _c_float, _c_float, _c_void_p],
+                       _c_int, _c_int, _c_float, _c_float, _c_int, _c_void_p],
     "ts_moe_down": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_qk_joint_norm_rope_store": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float,
+                                    _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_gla_scan": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_ll, _c_int, _c_void_p, _c_float, _c_float, _c_void_p, _c_void_p,
+                    _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_gla_norm_gate": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "ts_branch_norm_add": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float,
+                           _c_void_p],
+    "ts_stream_add": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "ts_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
 }
 
@@ -223,8 +231,8 @@ def _check_product(name: str, status: int, *tensors) -> None:
         _check(name, status)
 
 
-def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """hidden[t] = table[ids[t]] widened to float32.  hidden [T,H] f32, table [V,H], ids [T] i32."""
+def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
+    """hidden[t] = table[ids[t]] * scale, widened to float32.  hidden [T,H] f32, table [V,H], ids [T] i32."""
     flush_gemm_chain()
     _cuda_contig("hidden", hidden, torch.float32)
     _cuda_contig("table", table)
@@ -234,7 +242,7 @@ def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -
     if table.shape[1] != H or ids.numel() < T:
         raise KernelError(f"embed_gather: shapes disagree: hidden {tuple(hidden.shape)}, table {tuple(table.shape)}, ids {tuple(ids.shape)}")
     _check("embed_gather", _fn("ts_embed_gather")(
-        hidden.data_ptr(), table.data_ptr(), _act_code("table", table), ids.data_ptr(), T, H, V, _stream()))
+        hidden.data_ptr(), table.data_ptr(), _act_code("table", table), ids.data_ptr(), T, H, V, float(scale), _stream()))
 
 
 def feed_tokens(ids: torch.Tensor, source: torch.Tensor, lanes: torch.Tensor, rows: torch.Tensor, n: int) -> None:
@@ -393,11 +401,15 @@ def attention_paged_simple(
     head_dim: int,
     scale: float,
     window: int = 0,
+    chunk: int = 0,
+    sink: Optional[float] = None,
 ) -> None:
     """Causal attention over the paged cache on CUDA cores (float32 or bfloat16).
 
     q/out [T,nq*d]; caches [pages,page,nkv,d]; positions, seq_index [T] i32;
     block_table [B,max_blocks] i32.  window > 0: a query sees its last `window` keys.
+    chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks count
+    from position 0).  sink: a score that joins every softmax's denominator without a value.
     """
     flush_gemm_chain()
     _cuda_contig("q", q)
@@ -422,7 +434,8 @@ def attention_paged_simple(
     _check("attention_paged_simple", _fn("ts_attention_paged_simple")(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _act_code("q", q), out.data_ptr(),
         positions.data_ptr(), seq_index.data_ptr(), block_table.data_ptr(), block_table.shape[1],
-        page_size, T, nq, nkv, d, float(scale), int(window), _stream()))
+        page_size, T, nq, nkv, d, float(scale), int(window), int(chunk), 0 if sink is None else 1,
+        0.0 if sink is None else float(sink), _stream()))
 
 
 def sample(
@@ -544,6 +557,154 @@ def round_rows(rows: torch.Tensor, out: torch.Tensor) -> None:
     _check("round_rows", _fn("ts_round_rows")(rows.data_ptr(), _act_code("rows", rows), out.data_ptr(), _act_code("out", out), rows.numel(), _stream()))
 
 
+def branch_norm_add(branch: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor], hidden: torch.Tensor, eps: float,
+                    next_weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, next_eps: Optional[float] = None) -> None:
+    """hidden += branch * rsqrt(mean(branch^2) + eps) * weight (* scale, if given) in float32: a sublayer's
+    output norm and its per-channel scale on the way back into the stream.  With `next_weight` and
+    `out` the norm that reads the stream next runs in the same pass:
+    out = hidden * rsqrt(mean(hidden^2) + next_eps) * next_weight, in branch's element type (next_eps: eps unless given)."""
+    flush_gemm_chain()
+    _cuda_contig("branch", branch)
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("hidden", hidden, torch.float32)
+    T, H = hidden.shape
+    if branch.shape != hidden.shape or weight.numel() != H:
+        raise KernelError(f"branch_norm_add: shapes disagree: branch {tuple(branch.shape)}, hidden {tuple(hidden.shape)}, weight {tuple(weight.shape)}")
+    if scale is not None:
+        _cuda_contig("scale", scale, torch.float32)
+        if scale.numel() != H:
+            raise KernelError("branch_norm_add: scale must have one entry per channel")
+    if (next_weight is None) != (out is None):
+        raise KernelError("branch_norm_add: next_weight and out come together")
+    code = _act_code("branch", branch)
+    if out is not None:
+        _cuda_contig("next_weight", next_weight, torch.float32)
+        _cuda_contig("out", out, branch.dtype)
+        if out.shape != hidden.shape or next_weight.numel() != H:
+            raise KernelError("branch_norm_add: out must have hidden's shape and next_weight one entry per channel")
+    _check("branch_norm_add", _fn("ts_branch_norm_add")(
+        branch.data_ptr(), code, weight.data_ptr(), _ptr(scale), hidden.data_ptr(), _ptr(next_weight), _ptr(out), code, T, H, float(eps),
+        float(eps if next_eps is None else next_eps), _stream()))
+
+
+def stream_add(hidden: torch.Tensor, rows: Optional[torch.Tensor], vector: Optional[torch.Tensor]) -> None:
+    """hidden += rows (if given, [T, H] float32) + vector (if given, [H] float32), in float32."""
+    flush_gemm_chain()
+    _cuda_contig("hidden", hidden, torch.float32)
+    T, H = hidden.shape
+    if rows is not None:
+        _cuda_contig("rows", rows, torch.float32)
+        if rows.shape != hidden.shape:
+            raise KernelError("stream_add: rows must have hidden's shape")
+    if vector is not None:
+        _cuda_contig("vector", vector, torch.float32)
+        if vector.numel() != H:
+            raise KernelError("stream_add: vector must have one entry per channel")
+    _check("stream_add", _fn("ts_stream_add")(hidden.data_ptr(), _ptr(rows), _ptr(vector), T, H, _stream()))
+
+
+def qk_joint_norm_rope_store(qk: torch.Tensor, q_out: torch.Tensor, k_dst: torch.Tensor, v_dst: torch.Tensor,
+                             slot_mapping: Optional[torch.Tensor], q_norm_weight: torch.Tensor, k_norm_weight: torch.Tensor, eps: float,
+                             cos_sin: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """RMS norm over a token's whole q row and whole k row (one mean each over all heads' entries),
+    rotate-half rotation of every head's first entries, and the stores: q to q_out [T, nq*d], the
+    normed and rotated k to k_dst and the k row as projected to v_dst (cache pools [slots, nkv, d]
+    by `slot_mapping` [T] i32, -1 = skip; dense [T, nkv, d] without it).
+
+    qk [T, (nq + nkv) * d] with any row stride; norm weights [nq*d] and [nkv*d] float32; cos_sin
+    [T, rot/2, 2] float32 (the step's table) or None for no rotation."""
+    flush_gemm_chain()
+    nq, nkv, d = int(num_heads), int(num_kv_heads), int(head_dim)
+    if not qk.is_cuda or qk.dim() != 2 or qk.stride(1) != 1 or qk.shape[1] != (nq + nkv) * d:
+        raise KernelError(f"qk_joint_norm_rope_store: qk must be a CUDA matrix [T, {(nq + nkv) * d}] with unit inner stride, got {tuple(qk.shape)}")
+    T = qk.shape[0]
+    _cuda_contig("q_out", q_out, qk.dtype)
+    _cuda_contig("k_dst", k_dst, qk.dtype)
+    _cuda_contig("v_dst", v_dst, qk.dtype)
+    _cuda_contig("q_norm_weight", q_norm_weight, torch.float32)
+    _cuda_contig("k_norm_weight", k_norm_weight, torch.float32)
+    if q_out.numel() != T * nq * d or q_norm_weight.numel() != nq * d or k_norm_weight.numel() != nkv * d:
+        raise KernelError("qk_joint_norm_rope_store: q_out or the norm weights do not match the heads")
+    for name, c in (("k_dst", k_dst), ("v_dst", v_dst)):
+        if tuple(c.shape[-2:]) != (nkv, d):
+            raise KernelError(f"qk_joint_norm_rope_store: {name} must end in [{nkv},{d}], got {tuple(c.shape)}")
+        if slot_mapping is None and c.numel() < T * nkv * d:
+            raise KernelError(f"qk_joint_norm_rope_store: the dense {name} is too small")
+    if slot_mapping is not None:
+        _cuda_contig("slot_mapping", slot_mapping, torch.int32)
+        if slot_mapping.numel() < T:
+            raise KernelError("qk_joint_norm_rope_store: slot_mapping is shorter than the batch")
+    rot = 0
+    if cos_sin is not None:
+        _cuda_contig("cos_sin", cos_sin, torch.float32)
+        if cos_sin.dim() != 3 or cos_sin.shape[0] < T or cos_sin.shape[2] != 2:
+            raise KernelError(f"qk_joint_norm_rope_store: cos_sin must be [T, rot/2, 2], got {tuple(cos_sin.shape)}")
+        rot = 2 * cos_sin.shape[1]
+        if rot > d:
+            raise KernelError(f"qk_joint_norm_rope_store: rotary width {rot} does not fit head_dim {d}")
+    _check("qk_joint_norm_rope_store", _fn("ts_qk_joint_norm_rope_store")(
+        qk.data_ptr(), _act_code("qk", qk), qk.stride(0), q_out.data_ptr(), k_dst.data_ptr(), v_dst.data_ptr(), _ptr(slot_mapping),
+        q_norm_weight.data_ptr(), k_norm_weight.data_ptr(), float(eps), _ptr(cos_sin), rot, T, nq, nkv, d, _stream()))
+
+
+GLA_MAX_KEY_DIM = 1024
+
+
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor], tau: float, q_scale: float,
+             state: torch.Tensor, state_slots: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor, num_seqs: int, num_heads: int,
+             key_dim: int, value_dim: int) -> None:
+    """The recurrence of gated linear attention over the step's tokens, sequence by sequence:
+    decay = sigmoid(z + bias)^(1/tau) per key channel, S <- diag(decay) S + k v^T, out = S^T (q * q_scale).
+
+    q, k [T, H*d] and v [T, H*e]: views with one common row stride (columns of one product's result);
+    z [T, H*d] with its own; bias [H*d] float32 or None; state [slots, H, d, e] float32, read at a
+    sequence's slot before its first token of the step and written after its last; state_slots [B],
+    cu_seqlens [B+1] int32; out [T, H*e] float32.  Everything but the loads is float32."""
+    flush_gemm_chain()
+    H, d, e = int(num_heads), int(key_dim), int(value_dim)
+    if d > GLA_MAX_KEY_DIM:
+        raise KernelError(f"gla_scan: at most {GLA_MAX_KEY_DIM} key channels per head, got {d}")
+    T = q.shape[0]
+    for name, t, width in (("q", q, H * d), ("k", k, H * d), ("v", v, H * e), ("z", z, H * d)):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or tuple(t.shape) != (T, width) or t.dtype != q.dtype:
+            raise KernelError(f"gla_scan: {name} must be a CUDA matrix [{T}, {width}] of {q.dtype} with unit inner stride, got {tuple(t.shape)} {t.dtype}")
+    if not (q.stride(0) == k.stride(0) == v.stride(0)):
+        raise KernelError("gla_scan: q, k and v must share one row stride")
+    _cuda_contig("state", state, torch.float32)
+    _cuda_contig("state_slots", state_slots, torch.int32)
+    _cuda_contig("cu_seqlens", cu_seqlens, torch.int32)
+    _cuda_contig("out", out, torch.float32)
+    if tuple(state.shape[1:]) != (H, d, e) or out.shape != (T, H * e):
+        raise KernelError(f"gla_scan: state must be [slots, {H}, {d}, {e}] and out [{T}, {H * e}], got {tuple(state.shape)} and {tuple(out.shape)}")
+    if state_slots.numel() < num_seqs or cu_seqlens.numel() < num_seqs + 1:
+        raise KernelError("gla_scan: state_slots and cu_seqlens are shorter than the batch")
+    if bias is not None:
+        _cuda_contig("bias", bias, torch.float32)
+        if bias.numel() != H * d:
+            raise KernelError("gla_scan: the bias must have one entry per key channel")
+    _check("gla_scan", _fn("ts_gla_scan")(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), z.data_ptr(), z.stride(0), _act_code("q", q), _ptr(bias), float(tau),
+        float(q_scale), state.data_ptr(), state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, d, e, _stream()))
+
+
+def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_heads: int, value_dim: int, eps: float) -> None:
+    """out[t, h] = o[t, h] * rsqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per head of `value_dim`
+    entries.  o [T, H*e] float32; gate [T, H*e] (any row stride) and out [T, H*e] in the compute type;
+    weight [e] float32, the same for every head."""
+    flush_gemm_chain()
+    H, e = int(num_heads), int(value_dim)
+    _cuda_contig("o", o, torch.float32)
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("out", out)
+    T = o.shape[0]
+    if not gate.is_cuda or gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (T, H * e) or gate.dtype != out.dtype:
+        raise KernelError(f"gla_norm_gate: gate must be a CUDA matrix [{T}, {H * e}] of {out.dtype}, got {tuple(gate.shape)} {gate.dtype}")
+    if o.shape != (T, H * e) or out.shape != (T, H * e) or weight.numel() != e:
+        raise KernelError("gla_norm_gate: shapes disagree")
+    _check("gla_norm_gate", _fn("ts_gla_norm_gate")(o.data_ptr(), gate.data_ptr(), gate.stride(0), _act_code("out", out), weight.data_ptr(),
+                                                    out.data_ptr(), T, H, e, float(eps), _stream()))
+
+
 ROTARY_PAIRINGS = {"half": 0, "neighbours": 1}
 LATENT_SIMPLE_MAX_KEY_DIM = 1024
 
@@ -660,9 +821,24 @@ MOE_ROW_TILE = 64
 MOE_MAX_EXPERTS = 4096
 
 
-def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor) -> None:
-    """Per row of float32 logits [T, E]: the `top` experts with the largest sigmoid scores into ids
-    [T, top] i32 and their scores into weights [T, top] f32 (divided by their sum if `renormalize`)."""
+ROUTER_SCORES = {"sigmoid": 0, "softmax_chosen": 1}
+
+
+def _router_bias(name: str, bias: Optional[torch.Tensor], E: int) -> Optional[int]:
+    if bias is None:
+        return None
+    _cuda_contig("bias", bias, torch.float32)
+    if bias.numel() != E:
+        raise KernelError(f"{name}: the bias must have one entry per expert ({E}), got {tuple(bias.shape)}")
+    return bias.data_ptr()
+
+
+def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, score: str = "sigmoid") -> None:
+    """Per row of float32 logits [T, E] (+ bias [E], if given): the `top` experts with the largest
+    logits into ids [T, top] i32 and their weights into weights [T, top] f32.  score "sigmoid": the
+    weights are sigmoid(logit) (divided by their sum if `renormalize`); "softmax_chosen": the softmax
+    over the chosen logits alone."""
     flush_gemm_chain()
     _cuda_contig("logits", logits, torch.float32)
     _cuda_contig("ids", ids, torch.int32)
@@ -670,12 +846,14 @@ def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Te
     T, E = logits.shape
     if not 0 < top <= E or ids.numel() != T * top or weights.numel() != T * top:
         raise KernelError(f"router_topk: top {top} of {E} experts, ids {tuple(ids.shape)}, weights {tuple(weights.shape)}")
-    _check("router_topk", _fn("ts_router_topk")(logits.data_ptr(), T, E, int(top), int(bool(renormalize)), ids.data_ptr(), weights.data_ptr(), _stream()))
+    _check("router_topk", _fn("ts_router_topk")(logits.data_ptr(), _router_bias("router_topk", bias, E), T, E, int(top),
+                                                int(bool(renormalize)), ROUTER_SCORES[score], ids.data_ptr(), weights.data_ptr(), _stream()))
 
 
-def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor) -> None:
+def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
+           bias: Optional[torch.Tensor] = None, score: str = "sigmoid") -> None:
     """Logits and choice in one kernel: rows [T, W] (float32, or bfloat16 widened on the fly) against
-    router_weight [E, W] float32 with float32 sums, then as router_topk."""
+    router_weight [E, W] float32 with float32 sums (+ bias [E] float32, if given), then as router_topk."""
     flush_gemm_chain()
     _cuda_contig("rows", rows)
     _cuda_contig("router_weight", router_weight, torch.float32)
@@ -685,8 +863,9 @@ def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormaliz
     E = router_weight.shape[0]
     if router_weight.shape[1] != W or not 0 < top <= E or ids.numel() != T * top or weights.numel() != T * top:
         raise KernelError(f"router: rows {tuple(rows.shape)}, router {tuple(router_weight.shape)}, top {top}, ids {tuple(ids.shape)}")
-    _check("router", _fn("ts_router")(rows.data_ptr(), _act_code("rows", rows), router_weight.data_ptr(), T, W, E, int(top),
-                                      int(bool(renormalize)), ids.data_ptr(), weights.data_ptr(), _stream()))
+    _check("router", _fn("ts_router")(rows.data_ptr(), _act_code("rows", rows), router_weight.data_ptr(), _router_bias("router", bias, E),
+                                      T, W, E, int(top), int(bool(renormalize)), ROUTER_SCORES[score], ids.data_ptr(), weights.data_ptr(),
+                                      _stream()))
 
 
 # TS_MOE_MMA=0 (for measurements): bfloat16 expert products on CUDA cores too.
@@ -743,9 +922,13 @@ def _moe_path(name: str, plan, dtype: torch.dtype, *inner_widths: int) -> bool:
     raise KernelError(f"{name}: the plan was made for row tiles of {plan[3]}, which no kernel for {dtype} and inner widths {inner_widths} takes")
 
 
+MOE_ACTIVATIONS = {"capped_glu": 0, "swiglu": 1}
+
+
 def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple, gate: torch.Tensor,
-                up: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float) -> None:
-    """For every pair, in the plan's order: act[place] = capped_glu(gate_e (w x[token]), up_e (w x[token])).
+                up: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float, activation: str = "capped_glu") -> None:
+    """For every pair, in the plan's order: act[place] = activation(gate_e (w x[token]), up_e (w x[token])), where
+    activation is "capped_glu" (with `limit` and `alpha`) or "swiglu" (silu(gate) * up).
     x [T, K]; pair_weight [T*top] f32; gate, up [E, I, K]; act [T*top, I]."""
     flush_gemm_chain()
     offsets, tile_offsets, order, _ = plan
@@ -762,11 +945,11 @@ def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple, gate: t
     if _moe_path("moe_gate_up", plan, x.dtype, K):
         _check("moe_gate_up", _fn("ts_moe_gate_up_mma")(
             x.data_ptr(), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), gate.data_ptr(),
-            up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), plan[3], _stream()))
+            up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), MOE_ACTIVATIONS[activation], plan[3], _stream()))
         return
     _check("moe_gate_up", _fn("ts_moe_gate_up")(
         x.data_ptr(), _act_code("x", x), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(),
-        gate.data_ptr(), up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), _stream()))
+        gate.data_ptr(), up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), MOE_ACTIVATIONS[activation], _stream()))
 
 
 def moe_down(act: torch.Tensor, plan: tuple, down: torch.Tensor, pair_out: torch.Tensor) -> None:
@@ -1680,7 +1863,8 @@ _TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu"
           "sample", "sgemm_nt", "attention_paged_mma", "attention_decode_flat", "attention_prefill_tcgen05", "gemm_skinny_bf16",
           "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm", "sgemm_nt_batched", "library_bmm", "pair_hash_embed",
           "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "latent_attention_mma", "gelu_tanh", "capped_glu", "gelu_gate_rows",
-          "router_topk", "router", "moe_plan", "moe_gate_up", "moe_down", "moe_combine")
+          "router_topk", "router", "moe_plan", "moe_gate_up", "moe_down", "moe_combine", "branch_norm_add", "stream_add",
+          "qk_joint_norm_rope_store", "gla_scan", "gla_norm_gate")
 _plain_functions: dict[str, object] = {}
 _kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
 

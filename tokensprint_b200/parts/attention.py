@@ -34,6 +34,16 @@ class AttentionMixer(Mixer):
     (default head_dim^-0.5, engine/nn/sdpa.py:56), `position` (a position-encoding spec or
     None) and the checkpoint names of the tensors.  q, k, v weights are stacked at load
     into one [(nq + 2 nkv) d, H] matrix.
+
+    Further options, each free of the others:
+    `qk_norm` = "joint": one RMS norm over a token's whole q projection and one over its whole k
+    projection, before they are cut into heads (weights of nq*d and nkv*d entries), instead of a
+    norm per head (True or "head").
+    `values` = "keys": there is no value projection; a token's values are its key projection as it
+    comes, before norm and rotation (`v` is then no tensor name).
+    `chunk` = n: a query sees only the keys of its own block of n positions (blocks count from
+    position 0 of the sequence); the cache gives the pages of earlier blocks back.
+    `sink` = s: every softmax's denominator also holds exp(s), a key without a value.
     """
 
     folds_norms = True
@@ -51,16 +61,30 @@ class AttentionMixer(Mixer):
         head_dim: int,
         q: str,
         k: str,
-        v: str,
         o: str,
-        qk_norm: bool = False,
+        v: Optional[str] = None,
+        qk_norm: "bool | str" = False,
         qk_norm_eps: float = 1e-6,
         q_norm: Optional[str] = None,
         k_norm: Optional[str] = None,
         window: int = 0,
         scale: Optional[float] = None,
         position: Optional[PartSpec] = None,
+        values: str = "projection",
+        chunk: int = 0,
+        sink: Optional[float] = None,
     ) -> None:
+        if qk_norm is True:
+            qk_norm = "head"
+        if qk_norm not in (False, "head", "joint"):
+            raise ValueError(f"attention: qk_norm must be False, 'head' or 'joint', got {qk_norm!r}")
+        if values not in ("projection", "keys"):
+            raise ValueError(f"attention: values must be 'projection' or 'keys', got {values!r}")
+        if (values == "projection") != (v is not None):
+            raise ValueError("attention: a value projection needs its tensor's name, and values = 'keys' has none")
+        if (qk_norm == "joint") != (values == "keys"):
+            # the two come as one kernel (the whole-row norm with the unnormed keys as values)
+            raise ValueError("attention: qk_norm = 'joint' and values = 'keys' are offered together only")
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} heads are no multiple of {num_kv_heads} key/value heads")
         if qk_norm and (q_norm is None or k_norm is None):
@@ -68,13 +92,21 @@ class AttentionMixer(Mixer):
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.num_kv_heads, self.head_dim = int(num_kv_heads), int(head_dim)
         self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)
-        self.window = int(window or 0)
+        self.joint_norm, self.values_are_keys = qk_norm == "joint", values == "keys"
+        self.window, self.chunk = int(window or 0), int(chunk or 0)
+        self.sink = None if sink is None else float(sink)
+        if self.chunk < 0:
+            raise ValueError("attention: chunk must not be negative")
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.names = {"q": q, "k": k, "v": v, "o": o, "q_norm": q_norm, "k_norm": k_norm}
         self.position = build_part("position_encoding", position, ctx) if position is not None else None
         # the kernels of this mixer read everything a step needs from device memory; a position
         # encoding that rewrites q and k itself decides for itself
         self.graph_safe = self.position is None or self.position.graph_safe
+        if self.joint_norm:
+            self.folds_norms = False  # its q/k kernel is a step of its own
+            if self.position is not None and self.position.rotary_inv_freq() is None:
+                raise ValueError("attention: the joint q/k norm takes a rotate-half rotation (or none)")
         self.dtype = ctx.dtype
         self.qkv_weight: Optional[torch.Tensor] = None
         self.o_weight: Optional[torch.Tensor] = None
@@ -85,27 +117,32 @@ class AttentionMixer(Mixer):
         return self.qkv_weight
 
     def cache_need(self) -> CacheNeed:
-        kind = "window" if self.window > 0 else "full"
-        return CacheNeed(kind=kind, window=self.window, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+        if self.window > 0:  # (a layer with both bounds keeps what its window needs)
+            return CacheNeed(kind="window", window=self.window, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+        if self.chunk > 0:
+            return CacheNeed(kind="chunk", window=self.chunk, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+        return CacheNeed(kind="full", kv_heads=self.num_kv_heads, head_dim=self.head_dim)
 
     def tensor_specs(self) -> list[TensorSpec]:
         H, nq, nkv, d = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
         specs = [
             TensorSpec(self.names["q"], (nq * d, H)),
             TensorSpec(self.names["k"], (nkv * d, H)),
-            TensorSpec(self.names["v"], (nkv * d, H)),
             TensorSpec(self.names["o"], (H, nq * d)),
         ]
+        if not self.values_are_keys:
+            specs.insert(2, TensorSpec(self.names["v"], (nkv * d, H)))
         if self.qk_norm:
-            specs.append(TensorSpec(self.names["q_norm"], (d,), "vector"))
-            specs.append(TensorSpec(self.names["k_norm"], (d,), "vector"))
+            specs.append(TensorSpec(self.names["q_norm"], (nq * d if self.joint_norm else d,), "vector"))
+            specs.append(TensorSpec(self.names["k_norm"], (nkv * d if self.joint_norm else d,), "vector"))
         if self.position is not None:
             specs.extend(self.position.tensor_specs())
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
-        self.qkv_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        stacked = [tensors[n["q"]], tensors[n["k"]]] + ([] if self.values_are_keys else [tensors[n["v"]]])
+        self.qkv_weight = torch.cat(stacked, dim=0).contiguous()
         self.o_weight = tensors[n["o"]]
         if self.qk_norm:
             self.q_norm_weight = tensors[n["q_norm"]]
@@ -127,6 +164,8 @@ class AttentionMixer(Mixer):
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         tables = step.groups[cache.group]
         q = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
+        if self.joint_norm:
+            return self._forward_joint(x, q, step, cache, tables)
         inv_freq = self.position.rotary_inv_freq() if self.position is not None else None
         fused = self.position is None or inv_freq is not None
         if (fused and cache.writes and d == ops.GEMM_QK_ROPE_HEAD_DIM and (inv_freq is None or inv_freq.numel() == d // 2)
@@ -160,11 +199,30 @@ class AttentionMixer(Mixer):
             return linear_into_residual(out, self.o_weight, fold, next_weight=step.weight_after)
         return linear(out, self.o_weight, next_weight=step.weight_after)
 
+    def _forward_joint(self, x, q, step: StepContext, cache: LayerCache, tables):
+        """The whole-row q/k norm with the key projection as values: one product for [q | k], one
+        kernel for both norms, the rotation and the stores, attention, the output product."""
+        T = q.shape[0]
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        qk = linear_scaled(x, self.qkv_weight, next_weight=self.o_weight)
+        cos_sin = self.position.rotary_cos_sin(step) if self.position is not None else None
+        if cache.writes:
+            ops.qk_joint_norm_rope_store(qk, q, cache.k_pages, cache.v_pages, tables.slot_mapping, self.q_norm_weight,
+                                         self.k_norm_weight, self.qk_norm_eps, cos_sin, nq, nkv, d)
+        else:  # reads a cache that another run filled: only the queries are kept
+            k_tmp = torch.empty((T, nkv, d), device=q.device, dtype=q.dtype)
+            ops.qk_joint_norm_rope_store(qk, q, k_tmp, torch.empty_like(k_tmp), None, self.q_norm_weight, self.k_norm_weight,
+                                         self.qk_norm_eps, cos_sin, nq, nkv, d)
+        out = torch.empty((T, nq * d), device=q.device, dtype=q.dtype)
+        self._attend(q, out, step, cache, tables)
+        return linear(out, self.o_weight, next_weight=step.weight_after)
+
     # -- attention proper ---------------------------------------------------
 
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
-        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
+        plain_mask = self.chunk == 0 and self.sink is None
+        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d) and plain_mask:
             B, singles = step.num_seqs, step.decode_seqs
             few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
             if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):
@@ -197,7 +255,7 @@ class AttentionMixer(Mixer):
         # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
             q, cache.k_pages, cache.v_pages, out, step.positions, step.seq_index, tables.block_table,
-            step.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
+            step.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window, self.chunk, self.sink)
 
     def _attend_decode(self, q, out, step: StepContext, cache: LayerCache, tables, first: int, count: int, max_q: int) -> None:
         """Sequences [first, first + count) of the batch, each with at most `max_q` tokens (few enough

@@ -36,6 +36,8 @@ class TensorSpec:
 
     role: "matrix" is cast to the compute dtype; "vector" is held in float32 (a stored
     float32 stays exact, a stored bfloat16 widens without loss); "table" is held as int32.
+    An extent of -1 in `shape` stands for a size that no configuration key gives: the checkpoint's
+    own extent is taken (the part reads it from the loaded tensor and checks what must agree).
     """
 
     name: str
@@ -48,8 +50,10 @@ class CacheNeed:
     """What one run of a mixer needs from the cache manager.
 
     kind "full": all keys stay; "window": keys older than `window` positions before the
-    next query may be given back; "none": no pages.  `state_shape` asks for a slot of
-    that fixed shape per request (None: no state).
+    next query may be given back; "chunk": queries see only the keys of their own block of
+    `window` positions (blocks count from position 0), so the pages before the block of the next
+    query may be given back; "none": no pages.  `state_shape` asks for a slot of that fixed shape
+    per request (None: no state).
 
     What is paged per token: `k_row` is the shape of one token's entry in the first pool and
     `v_row` that of the second pool (None: the mixer pages one tensor only, e.g. a latent).  The
@@ -83,7 +87,7 @@ class CacheNeed:
 
     @property
     def group_key(self) -> tuple[str, int]:
-        return (self.kind, self.window if self.kind == "window" else 0)
+        return (self.kind, self.window if self.kind in ("window", "chunk") else 0)
 
     @property
     def token_elements(self) -> int:
@@ -182,6 +186,15 @@ class Rounded:
     """The rows of the (complete) residual stream once more in the compute dtype, left by the kernel
     that last wrote them: what a block whose sublayers read the stream itself hands to the next
     one in place of a pending branch, so that nobody has to round the rows again."""
+
+    x: torch.Tensor
+
+
+@dataclass
+class Normed:
+    """The input of the next block's entry norm, done: `x` = that norm of the (complete) residual
+    stream, in the compute dtype, left by the kernel that last added into the stream (a block may
+    return one when `step.norm_after` names the norm; `hidden` then lacks nothing)."""
 
     x: torch.Tensor
 

@@ -11,6 +11,7 @@ from tokensprint_b200.parts.base import (
     Block,
     BuildContext,
     LayerCache,
+    Normed,
     PartSpec,
     PreNormed,
     ResidualNorm,
@@ -70,6 +71,8 @@ class PreNormBlock(Block):
 
         if isinstance(pending, PreNormed) and mixer_folds:
             x = pending
+        elif isinstance(pending, Normed):  # the block before ran this block's first norm with its last kernel
+            x = pending.x
         else:
             x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
             self._before(self.mixer_norm)
@@ -174,3 +177,100 @@ class PostNormBlock(Block):
             x = self._add(norm, branch, hidden)
         step.weight_after = after_block
         return None if self.dtype == torch.float32 else Rounded(x)
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """h = h + s_a * Norm_ao(Mixer(Norm_a(h))); h = h + s_f * Norm_fo(FeedForward(Norm_f(h))).
+
+    Every sublayer stands between two norms, and what its output norm leaves is multiplied
+    channel by channel by a learned scale (`mixer_scale`, `ffn_scale`: names of [width] vectors,
+    or None) before it joins the float32 stream.  The feed-forward with its norms and scale may be
+    absent.  The output norms are plain RMS norms; one kernel runs such a norm on the branch, the
+    scale, the sum into the stream and the norm that reads the stream next (this block's
+    feed-forward norm, or the first norm of the block that follows, which is then handed the
+    finished rows as a `Normed`)."""
+
+    def __init__(self, ctx: BuildContext, *, mixer: PartSpec, mixer_norm: PartSpec, mixer_out_norm: PartSpec, hidden_size: int,
+                 mixer_scale: Optional[str] = None, feed_forward: Optional[PartSpec] = None, ffn_norm: Optional[PartSpec] = None,
+                 ffn_out_norm: Optional[PartSpec] = None, ffn_scale: Optional[str] = None) -> None:
+        if not ((feed_forward is None) == (ffn_norm is None) == (ffn_out_norm is None)):
+            raise ValueError("sandwich_norm block: a feed-forward comes with both of its norms")
+        if feed_forward is None and ffn_scale is not None:
+            raise ValueError("sandwich_norm block: a scale without its feed-forward")
+        self.dtype, self.hidden_size = ctx.dtype, int(hidden_size)
+        self.mixer = build_part("mixer", mixer, ctx)
+        self.mixer_norm = build_part("norm", mixer_norm, ctx)
+        self.mixer_out_norm = build_part("norm", mixer_out_norm, ctx)
+        self.feed_forward = None if feed_forward is None else build_part("feed_forward", feed_forward, ctx)
+        self.ffn_norm = None if ffn_norm is None else build_part("norm", ffn_norm, ctx)
+        self.ffn_out_norm = None if ffn_out_norm is None else build_part("norm", ffn_out_norm, ctx)
+        self.scale_names = {"mixer": mixer_scale, "ffn": ffn_scale}
+        self.mixer_scale: Optional[torch.Tensor] = None
+        self.ffn_scale: Optional[torch.Tensor] = None
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.ffn_norm, self.feed_forward, self.ffn_out_norm)
+                            if p is not None)
+        self.graph_safe = all(p.graph_safe for p in self._parts)
+        self.reads_through_ops = True
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        specs = [s for p in self._parts for s in p.tensor_specs()]
+        specs += [TensorSpec(name, (self.hidden_size,), "vector") for name in self.scale_names.values() if name is not None]
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for p in self._parts:
+            p.load(tensors)
+        if self.scale_names["mixer"] is not None:
+            self.mixer_scale = tensors[self.scale_names["mixer"]]
+        if self.scale_names["ffn"] is not None:
+            self.ffn_scale = tensors[self.scale_names["ffn"]]
+        for norm in (self.mixer_out_norm, self.ffn_out_norm):
+            if norm is not None and norm.params() is None:
+                raise ValueError("sandwich_norm block: the norm on a sublayer's output must be a plain RMS norm")
+
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def first_weight(self):
+        return self.mixer.first_weight()
+
+    def _close(self, branch: torch.Tensor, out_norm, scale: Optional[torch.Tensor], hidden: torch.Tensor, next_norm):
+        """Output norm, scale and the sum into the stream; with `next_norm` (a plain RMS norm) also
+        that norm of the new rows, which are returned."""
+        p = out_norm.params()
+        nxt = next_norm.params() if next_norm is not None else None
+        if nxt is None:
+            ops.branch_norm_add(branch, p.weight, scale, hidden, p.eps)
+            return None
+        out = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+        ops.branch_norm_add(branch, p.weight, scale, hidden, p.eps, next_weight=nxt.weight, out=out, next_eps=nxt.eps)
+        return out
+
+    def forward(self, hidden, pending, step: StepContext, cache: LayerCache):
+        after_block, norm_after = step.weight_after, step.norm_after
+        if isinstance(pending, torch.Tensor):  # a branch that the block before did not add
+            ops.residual_add(hidden, pending)
+            pending = None
+        if isinstance(pending, Normed):
+            x = pending.x
+        else:  # the stream is complete (nothing pending, or rows prepared for a kernel this block does not use)
+            x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+            PreNormBlock._before(self.mixer_norm)
+            self.mixer_norm.forward(hidden, None, x)
+        step.weight_after = (self.feed_forward.first_weight() if self.feed_forward is not None else None) or after_block
+        PreNormBlock._before(self.mixer)
+        branch = self.mixer.forward(x, step, cache)
+        step.weight_after = after_block
+        if self.feed_forward is not None:
+            x = self._close(branch, self.mixer_out_norm, self.mixer_scale, hidden, self.ffn_norm)
+            if x is None:  # a feed-forward norm of another kind: a step of its own
+                x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+                PreNormBlock._before(self.ffn_norm)
+                self.ffn_norm.forward(hidden, None, x)
+            PreNormBlock._before(self.feed_forward)
+            branch = self.feed_forward.forward(x, step)
+            out = self._close(branch, self.ffn_out_norm, self.ffn_scale, hidden, norm_after)
+        else:
+            out = self._close(branch, self.mixer_out_norm, self.mixer_scale, hidden, norm_after)
+        return None if out is None else Normed(out)

@@ -81,12 +81,17 @@ class CappedGLUFeedForward(FeedForward):
 
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
-    """`num_experts` capped-GLU experts of which each token uses `top`:
+    """`num_experts` gated experts of which each token uses `top`:
 
-        s = sigmoid(W_router x)  (float32; from the float32 residual rows where the block has them)
-        chosen = the `top` largest scores, weights w_e = s_e (or s_e / their sum with `renormalize`)
+        z = W_router x (+ b, if `router_bias` names one)   (float32; from the float32 residual rows
+                                                            where the block has them)
+        chosen = the `top` largest logits
+        weights: `score` "sigmoid": w_e = sigmoid(z_e) (or that / their sum with `renormalize`);
+                 "softmax_chosen": the softmax over the chosen logits alone
         f = sum over chosen e of expert_e(w_e x)   (`weight_on` "input"; "output": w_e expert_e(x))
             + shared(x) if a shared expert is named (any feed-forward spec)
+        expert(x) = W_down act(W_gate x, W_up x), `activation` "capped_glu" (with `limit`, `alpha`)
+                    or "swiglu" (silu(gate) * up)
 
     Routing, the sort of the (token, choice) pairs by expert and both expert products run on the
     device with grids that depend on the token count only, so a decode step is a fixed kernel
@@ -96,9 +101,10 @@ class RoutedExperts(FeedForward):
     graph_safe = True
     wants_residual = True
 
-    def __init__(self, ctx: BuildContext, *, hidden_size: int, num_experts: int, top: int, intermediate_size: int, limit: float,
-                 router: str, expert_prefix: str, alpha: float = 1.702, renormalize: bool = False, weight_on: str = "input",
-                 shared: Optional[PartSpec] = None) -> None:
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, num_experts: int, top: int, intermediate_size: int,
+                 router: str, expert_prefix: str, limit: float = 0.0, alpha: float = 1.702, renormalize: bool = False,
+                 weight_on: str = "input", shared: Optional[PartSpec] = None, router_bias: Optional[str] = None,
+                 score: str = "sigmoid", activation: str = "capped_glu") -> None:
         self.hidden_size, self.num_experts, self.top = int(hidden_size), int(num_experts), int(top)
         self.intermediate_size, self.limit, self.alpha = int(intermediate_size), float(limit), float(alpha)
         self.renormalize = bool(renormalize)
@@ -106,8 +112,13 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"routed experts: top {top} of {num_experts} experts")
         if weight_on not in ("input", "output"):
             raise ValueError(f"routed experts: weight_on must be 'input' or 'output', got {weight_on!r}")
-        self.weight_on = weight_on
-        self.router_name, self.prefix = router, expert_prefix
+        if score not in ops.ROUTER_SCORES:
+            raise ValueError(f"routed experts: score must be one of {sorted(ops.ROUTER_SCORES)}, got {score!r}")
+        if activation not in ops.MOE_ACTIVATIONS:
+            raise ValueError(f"routed experts: activation must be one of {sorted(ops.MOE_ACTIVATIONS)}, got {activation!r}")
+        self.weight_on, self.score, self.activation = weight_on, score, activation
+        self.router_name, self.router_bias_name, self.prefix = router, router_bias, expert_prefix
+        self.router_bias: Optional[torch.Tensor] = None
         self.shared = build_part("feed_forward", shared, ctx) if shared is not None else None
         if self.shared is not None:
             self.graph_safe = self.shared.graph_safe
@@ -124,6 +135,8 @@ class RoutedExperts(FeedForward):
     def tensor_specs(self) -> list[TensorSpec]:
         H, I = self.hidden_size, self.intermediate_size
         specs = [TensorSpec(self.router_name, (self.num_experts, H), "vector")]  # the router stays float32
+        if self.router_bias_name is not None:
+            specs.append(TensorSpec(self.router_bias_name, (self.num_experts,), "vector"))
         for e in range(self.num_experts):
             g, u, d = self._expert_names(e)
             specs += [TensorSpec(g, (I, H)), TensorSpec(u, (I, H)), TensorSpec(d, (H, I))]
@@ -133,6 +146,8 @@ class RoutedExperts(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.router = tensors[self.router_name]
+        if self.router_bias_name is not None:
+            self.router_bias = tensors[self.router_bias_name]
         names = [self._expert_names(e) for e in range(self.num_experts)]
         self.gate = torch.stack([tensors[g] for g, _, _ in names]).contiguous()
         self.up = torch.stack([tensors[u] for _, u, _ in names]).contiguous()
@@ -145,14 +160,15 @@ class RoutedExperts(FeedForward):
         rows = residual if residual is not None else x  # float32 rows where the block has them, else their rounding
         chosen = torch.empty((T, top), device=dev, dtype=torch.int32)
         weights = torch.empty((T, top), device=dev, dtype=torch.float32)
-        ops.router(rows, self.router, top, self.renormalize, chosen, weights)
+        ops.router(rows, self.router, top, self.renormalize, chosen, weights, bias=self.router_bias, score=self.score)
         # both products take the same plan: the tensor cores only if both inner widths suit them
         tensor_cores = ops.moe_on_tensor_cores(x.dtype, self.hidden_size, self.intermediate_size)
         plan = ops.moe_plan(chosen, self.num_experts, ops.moe_row_tile(tensor_cores, T * top, self.num_experts))
         act = torch.empty((T * top, self.intermediate_size), device=dev, dtype=x.dtype)
         on_input = self.weight_on == "input"
         ones = None if on_input else torch.ones((T * top,), device=dev, dtype=torch.float32)
-        ops.moe_gate_up(x, weights.view(-1) if on_input else ones, plan, self.gate, self.up, act, top, self.limit, self.alpha)
+        ops.moe_gate_up(x, weights.view(-1) if on_input else ones, plan, self.gate, self.up, act, top, self.limit, self.alpha,
+                        activation=self.activation)
         pair_out = torch.empty((T * top, self.hidden_size), device=dev, dtype=x.dtype)
         ops.moe_down(act, plan, self.down, pair_out)
         shared = None

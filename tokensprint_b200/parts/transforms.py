@@ -45,3 +45,39 @@ class PairHashEmbedding(Transform):
         ops.pair_hash_embed(x, self.table, step.token_ids, step.positions, step.seq_index, step.cu_seqlens_q, step.state_slots,
                             cache.state.view(-1), self.buckets, self.mul_prev, self.mul_cur, self.vocab_size)
         return x
+
+
+@register_part("transform", "pass_entry")
+class PassEntry(Transform):
+    """What a model adds to the residual stream where a stretch of layers begins (a model that runs
+    a stretch several times names one of these before each pass):
+
+        x += embedding rows   (with `add_embedding`: the rows as they entered the first block)
+        x += table[row]       (one learned vector of the [rows, width] tensor `table` per pass)
+
+    both in float32, in one kernel."""
+
+    graph_safe = True
+    reads_through_ops = True
+
+    def __init__(self, ctx: BuildContext, *, table: Optional[str], rows: int, row: int, hidden_size: int, add_embedding: bool) -> None:
+        self.name, self.rows, self.row, self.hidden_size = table, int(rows), int(row), int(hidden_size)
+        self.add_embedding = bool(add_embedding)
+        if table is not None and not 0 <= self.row < self.rows:
+            raise ValueError(f"pass_entry: row {row} of a table of {rows} rows")
+        self.vector: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [] if self.name is None else [TensorSpec(self.name, (self.rows, self.hidden_size), "vector")]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        if self.name is not None:
+            keep = getattr(tensors, "keep", None)  # one copy of the table for all passes
+            table = keep(self.name) if keep is not None else tensors[self.name]
+            self.vector = table[self.row]
+
+    def forward(self, x: torch.Tensor, step: Optional[StepContext], embedding: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.add_embedding and embedding is None:
+            raise ops.KernelError("pass_entry: the embedding rows were not kept for this step")
+        ops.stream_add(x, embedding if self.add_embedding else None, self.vector)
+        return x

@@ -59,10 +59,13 @@ def check_tensors(
     ignorable = set(ignorable)
     missing = [n for n in wanted if n not in available]
     unexpected = [n for n in available if n not in wanted and n not in ignorable]
+    def fits(found: Sequence[int], want: Sequence[int]) -> bool:  # an extent of -1 takes what the checkpoint has
+        return len(found) == len(want) and all(w == -1 or f == w for f, w in zip(found, want))
+
     wrong = [
         f"{n}: expected {list(wanted[n].shape)}, found {list(available[n])}"
         for n in wanted
-        if n in available and tuple(available[n]) != tuple(wanted[n].shape)
+        if n in available and not fits(tuple(available[n]), tuple(wanted[n].shape))
     ]
     if missing or unexpected or wrong:
         raise WeightsError(sorted(missing), sorted(unexpected), wrong, where)
@@ -144,6 +147,9 @@ class RandomSource(WeightSource):
         generate_on_device: bool = False,
     ) -> None:
         self.specs = {s.name: s for s in specs}
+        open_extents = sorted(n for n, s in self.specs.items() if any(e < 0 for e in s.shape))
+        if open_extents:
+            raise ValueError(f"random weights need every extent; the configuration leaves open: {open_extents}")
         self.seed, self.std, self.vector_std = seed, std, vector_std
         self.generate_on_device = generate_on_device
         self.where = f"random weights (seed {seed})"
