@@ -407,7 +407,7 @@ def run_probe(args) -> int:
     if args.designs:  # the other design's named model (four layers at width 2,048)
         from tokensprint_b200.config.registry import get_model_config
 
-        cfg = get_model_config("fegetar-w2048")
+        cfg = get_model_config("dazilix-w2048" if args.designs == "dazilix" else "fegetar-w2048")
     else:
         d = get_preset_dict(MODEL_NAME)
         d["num_hidden_layers"] = args.layers or 4
@@ -742,9 +742,10 @@ def main() -> int:
                         "(the events cost host time: take the throughput from a run without this option)")
     p.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                    help="a serving loop through generate() instead of the decode benchmark (one JSON line)")
-    p.add_argument("--designs", action="store_true",
-                   help="Fegetar beside Qwen3 dense at equal size (a few layers of realistic widths, random weights): prompt and "
-                        "decode throughput and the attention kernels against their rooflines (one JSON line)")
+    p.add_argument("--designs", nargs="?", const="fegetar", default=None, choices=["fegetar", "dazilix"],
+                   help="another design beside Qwen3 dense at equal size (a few layers of realistic widths, random weights): prompt and "
+                        "decode throughput and the design's kernels against their rooflines (one JSON line); "
+                        "without a name: Fegetar")
     p.add_argument("--probe", choices=["decode", "prefill"], default=None,
                    help="run a few steps inside cudaProfilerStart/Stop for ncu and exit (see profiles/); with --designs: of Fegetar's named model")
     args = p.parse_args()
@@ -758,7 +759,7 @@ def main() -> int:
     if args.designs:
         from tokensprint_b200 import design_bench
 
-        result = design_bench.run(min(args.steps, 32), args.warmup, load_peaks())
+        result = design_bench.run(min(args.steps, 32), args.warmup, load_peaks(), which=args.designs)
     elif args.impl == "reference":
         result = run_reference(args)
     else:

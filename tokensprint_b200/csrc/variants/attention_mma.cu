@@ -65,6 +65,9 @@ struct AttnParams {
   int* error;                     // set to 1 when a bounded wait of the copy-engine path gave up
   float scale_log2;               // scale * log2(e)
   int num_seqs;                   // B
+  int chunk;                      // > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from position 0)
+  int has_sink;                   // 1: every softmax's denominator also holds exp(sink score): a key without a value
+  float sink_raw;                 // the sink's score divided by the scale (the running max is kept in raw score units)
   int* flat_prefix;               // even-share kernel: [B + 1] key blocks of the sequences before each one, left for its combine kernel
 };
 
@@ -75,6 +78,12 @@ struct AttnParams {
 #endif
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+// The first key a query at position `pos` sees: the start of its window, of its block of positions, or 0.
+__device__ __forceinline__ int first_visible_key(const AttnParams& p, int pos) {
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos / p.chunk * p.chunk);
+  return lo;
+}
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
@@ -289,7 +298,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   // Keys this tile can see at all.
   const int last_row = min(r0 + BM, rows_total) - 1;
   const int hi = start_pos + last_row / G;
-  const int lo = p.window > 0 ? max(0, start_pos + r0 / G - p.window + 1) : 0;
+  const int lo = first_visible_key(p, start_pos + r0 / G);
   int kb0 = lo / BN, kb1 = hi / BN;
   if (p.splits > 1) {
     const int per = p.keys_per_split > 0 ? p.keys_per_split / BN : (kb1 - kb0 + p.splits) / p.splits;
@@ -322,7 +331,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   for (int h = 0; h < 2; ++h) {
     const int r = r0 + warp_row0 + g + 8 * h;
     row_pos[h] = r < rows_total ? start_pos + r / G : -1;
-    row_lo[h] = (p.window > 0 && row_pos[h] >= 0) ? max(0, row_pos[h] - p.window + 1) : 0;
+    row_lo[h] = row_pos[h] >= 0 ? first_visible_key(p, row_pos[h]) : 0;
   }
   // Smallest position and largest window start among this warp's rows that exist: key blocks
   // between them are seen in full by every such row.  (Rows that do not exist are never
@@ -330,7 +339,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int warp_first_row = r0 + warp_row0;
   const int warp_last_row = min(warp_first_row + 15, rows_total - 1);
   const int warp_min_pos = warp_first_row < rows_total ? start_pos + warp_first_row / G : -1;
-  const int warp_max_lo = (p.window > 0 && warp_first_row < rows_total) ? max(0, start_pos + warp_last_row / G - p.window + 1) : 0;
+  const int warp_max_lo = warp_first_row < rows_total ? first_visible_key(p, start_pos + warp_last_row / G) : 0;
 
   // Copy-engine path: warp 0 asks for block `blk` (all its lanes together: every lane one box of
   // [page rows x 64 elements] of K or V), waiting first until the four warps are done with what
@@ -479,6 +488,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 #pragma unroll
     for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  if (p.has_sink && split == 0 && (!SPLIT_KEYS || warp == 0)) {
+    // The sink is a key of a fixed score and no value: exactly one of the partial softmaxes of a row
+    // starts from it (the first split's; of warps that share rows, the first warp's), and every merge
+    // downstream takes it along.  A row's sum is spread over the four threads of a quad: one of them holds it.
+    m_run[0] = m_run[1] = p.sink_raw;
+    l_run[0] = l_run[1] = tq == 0 ? 1.f : 0.f;
+  }
 
   unsigned q_frag[Q_IN_REGS ? D / 16 : 1][4];
   const __nv_bfloat16* q_warp = q_s + warp_row0 * LD;
@@ -863,7 +879,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
   const int last_row = min(r0 + PF_BM, rows_total) - 1;
   const int hi = start_pos + last_row / G;
   const int first_pos = start_pos + r0 / G;  // position of the tile's first row
-  const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int lo = first_visible_key(p, first_pos);
   const int kb0 = lo / BN, kb1 = hi / BN;
   const int nblocks = kb1 - kb0 + 1;
   const int* table = p.block_table + (size_t)b * p.max_blocks;
@@ -876,7 +892,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
     for (int h = 0; h < 2; ++h) {
       const int r = r0 + warp_row0 + mt * 16 + g + 8 * h;
       row_pos[mt][h] = r < rows_total ? start_pos + r / G : -1;
-      row_lo[mt][h] = (p.window > 0 && row_pos[mt][h] >= 0) ? max(0, row_pos[mt][h] - p.window + 1) : 0;
+      row_lo[mt][h] = row_pos[mt][h] >= 0 ? first_visible_key(p, row_pos[mt][h]) : 0;
     }
   // Positions of this warp's first and last row: blocks of keys between them need no mask.
   const int warp_first_pos = start_pos + min(r0 + warp_row0, rows_total - 1) / G;
@@ -907,8 +923,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
   float m_run[PF_MT][2], l_run[PF_MT][2];
 #pragma unroll
   for (int mt = 0; mt < PF_MT; ++mt) {
-    m_run[mt][0] = m_run[mt][1] = -INFINITY;
-    l_run[mt][0] = l_run[mt][1] = 0.f;
+    m_run[mt][0] = m_run[mt][1] = p.has_sink ? p.sink_raw : -INFINITY;  // the sink: a key of a fixed score and no value
+    l_run[mt][0] = l_run[mt][1] = (p.has_sink && tq == 0) ? 1.f : 0.f;       // (a row's sum is spread over a quad's threads)
   }
   const __nv_bfloat16* q_warp = q_s + warp_row0 * LD;
 
@@ -956,7 +972,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
     // A block whose last key is at or before the warp's first position, whose first key is
     // inside every row's window, and whose rows all exist needs no mask.
     const bool unmasked = warp_rows_valid && (kbase + BN - 1 <= warp_first_pos) &&
-                          (p.window <= 0 || kbase >= start_pos + (r0 + warp_row0 + 16 * PF_MT - 1) / G - p.window + 1);
+                          kbase >= first_visible_key(p, start_pos + (r0 + warp_row0 + 16 * PF_MT - 1) / G);
 #pragma unroll
     for (int mt = 0; mt < PF_MT; ++mt) {
       // Running max in raw score units (the scale is positive, so it commutes with max); the
@@ -1329,7 +1345,7 @@ __global__ void __launch_bounds__(128) attention_decode_flat_kernel(const AttnPa
     for (int h = 0; h < 2; ++h) {
       const int r = g + 8 * h;
       row_pos[h] = r < s.rows_total ? s.start_pos + r / G : -1;
-      row_lo[h] = (p.window > 0 && row_pos[h] >= 0) ? max(0, row_pos[h] - p.window + 1) : 0;
+      row_lo[h] = row_pos[h] >= 0 ? first_visible_key(p, row_pos[h]) : 0;
     }
     const int warp_min_pos = s.start_pos;
     const int warp_max_lo = p.window > 0 ? max(0, s.start_pos + (s.rows_total - 1) / G - p.window + 1) : 0;
@@ -1763,12 +1779,16 @@ TS_EXPORT int ts_attention_mma_decode_rows(void) { return 16; }
 static int ts_attention_last_launches = 0;
 TS_EXPORT int ts_attention_mma_last_launches(void) { return ts_attention_last_launches; }
 
-TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,
-                                           float* scratch, const int* cu_q, const int* ctx_len,
-                                           const int* block_table, const int* seq_index, int max_blocks,
-                                           int page, int T, int B, int max_q, int nq, int nkv, float scale,
-                                           int window, int splits, int keys_per_split, int* counters, void* stream_) {
+// `chunk` > 0: queries see only the keys of their own block of `chunk` positions; `has_sink`: exp(sink_score)
+// joins every softmax's denominator.  (The even-share decode kernel below knows neither.)
+TS_EXPORT int ts_attention_paged_mma_masked(const void* q, const void* kcache, const void* vcache, void* out,
+                                            float* scratch, const int* cu_q, const int* ctx_len,
+                                            const int* block_table, const int* seq_index, int max_blocks,
+                                            int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                            int window, int chunk, int has_sink, float sink_score, int splits, int keys_per_split,
+                                            int* counters, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
+  if (chunk < 0 || (has_sink && !(scale > 0.f))) return TS_ERR_BAD_ARGUMENT;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1 ||
       keys_per_split < 0 || keys_per_split % BN != 0)
     return TS_ERR_BAD_ARGUMENT;
@@ -1791,6 +1811,9 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
   p.nq = nq;
   p.nkv = nkv;
   p.window = window;
+  p.chunk = chunk;
+  p.has_sink = has_sink ? 1 : 0;
+  p.sink_raw = has_sink ? sink_score / scale : 0.f;
   p.splits = splits;
   p.keys_per_split = keys_per_split;
   p.counters = (counters != nullptr && splits > 1 && (long long)max_q * (nq / nkv) <= 16) ? counters : nullptr;
@@ -1824,6 +1847,15 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
     status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }
   return status;
+}
+
+TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,
+                                           float* scratch, const int* cu_q, const int* ctx_len,
+                                           const int* block_table, const int* seq_index, int max_blocks,
+                                           int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                           int window, int splits, int keys_per_split, int* counters, void* stream_) {
+  return ts_attention_paged_mma_masked(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index, max_blocks, page, T, B,
+                                       max_q, nq, nkv, scale, window, 0, 0, 0.f, splits, keys_per_split, counters, stream_);
 }
 
 TS_EXPORT int ts_attention_paged_mma_chunked(const void* q, const void* kcache, const void* vcache, void* out,
@@ -1894,6 +1926,9 @@ TS_EXPORT int ts_attention_decode_flat(const void* q, const void* kcache, const 
   p.nq = nq;
   p.nkv = nkv;
   p.window = window;
+  p.chunk = 0;
+  p.has_sink = 0;
+  p.sink_raw = 0.f;
   p.splits = 1;
   p.row_tiles = 1;
   p.num_seqs = B;

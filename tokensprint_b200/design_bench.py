@@ -5,6 +5,11 @@ at two batch sizes (graphs, as generation runs them), and the device time per ke
 eager prompt step and an eager decode step, with the attention kernels' distance from their
 rooflines (prompt: flops against the measured bf16 peak; decode: cache bytes against the measured
 copy bandwidth).  `python bench.py --designs` prints one JSON line.
+
+`python bench.py --designs dazilix` does the same for Dazilix (attention inside blocks of positions
+with a sink, gated linear attention, routed SwiGLU experts, every sublayer between two norms)
+beside Qwen3 dense at equal width, depth, heads and feed-forward weight per token, and adds the
+recurrent mixer's and the norm kernels' distance from their rooflines.
 """
 
 from __future__ import annotations
@@ -46,6 +51,34 @@ def qwen3_config(s: dict) -> dict:
     W = s["width"]
     inter = int(round(fegetar_ff_params(s) / (3 * W) / 64)) * 64  # SwiGLU of the same weight per token
     return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": s["layers"], "hidden_size": W,
+            "num_attention_heads": s["heads"], "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": inter, "vocab_size": VOCAB,
+            "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+            "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
+
+
+# Dazilix at the same widths: three attention layers and one recurrent layer, heads of 128, blocks of
+# positions long enough to hold the prompt (so that its attention does the work of the dense model's),
+# routed experts in every layer; the recurrent layer's state is [heads, 64, 128] float32 per request.
+DAZILIX_SIZES = {
+    "w2048": dict(width=2048, heads=16, layers=4, experts=16, top=2, expert_ff=1024, gla_dim=64, gla_vdim=128, block=4096),
+    "w4096": dict(width=4096, heads=32, layers=4, experts=32, top=4, expert_ff=1536, gla_dim=64, gla_vdim=128, block=4096),
+}
+DAZILIX_RECURRENT_LAYERS = (2,)
+
+
+def dazilix_config(s: dict) -> dict:
+    att = {"heads": s["heads"], "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 1000000.0, "dims": 64},
+           "mask": {"size": s["block"]}}
+    gla = {"heads": s["heads"], "dim": s["gla_dim"], "vdim": s["gla_vdim"], "tau": 16.0, "decay_rank": 16}
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"]}}
+    return {"architecture": "Dazilix", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [{"type": "gla", "mixer": gla, "mlp": moe} if i in DAZILIX_RECURRENT_LAYERS else {"type": "attention", "mixer": att, "mlp": moe}
+                       for i in range(s["layers"])]}
+
+
+def qwen3_beside_dazilix(s: dict) -> dict:
+    inter = int(round(s["top"] * s["expert_ff"] / 64)) * 64  # SwiGLU of the same weight per token as the chosen experts
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": s["layers"], "hidden_size": s["width"],
             "num_attention_heads": s["heads"], "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": inter, "vocab_size": VOCAB,
             "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 8192,
             "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
@@ -143,6 +176,11 @@ def _attention_rooflines(design: str, s: dict, m: dict, peaks: dict) -> dict[str
         names = ("latent_attention_mma",)
         flops = L * 2 * H * pairs * (576 + 512)
         row_bytes = 576 * 2
+    elif design == "dazilix":
+        L = s["layers"] - len(DAZILIX_RECURRENT_LAYERS)
+        names = ("attention_paged_mma",)
+        flops = L * 4 * H * 128 * pairs
+        row_bytes = 2 * 8 * 128 * 2
     else:
         names = ("attention_prefill_tcgen05", "attention_paged_mma", "attention_decode_flat")
         flops = L * 4 * H * 128 * pairs
@@ -164,7 +202,43 @@ def _attention_rooflines(design: str, s: dict, m: dict, peaks: dict) -> dict[str
     return out
 
 
-def run(steps: int, warmup: int, peaks: dict) -> dict[str, Any]:
+def _dazilix_rooflines(s: dict, m: dict, peaks: dict) -> dict[str, Any]:
+    """The recurrent mixer and the norm kernels of Dazilix against their rooflines, from the per-class
+    timers.  The recurrence: a prompt costs 6 float32 operations per state entry and token (decay,
+    outer product, read-out) against the FFMA rate of the SMs at their top clock; a decode step reads and
+    writes every request's state once, against the measured copy bandwidth.  The norm kernels move
+    the branch (bf16), the stream (float32, read and written) and the next sublayer's input (bf16)."""
+    out: dict[str, Any] = {}
+    L, H, d, e, W = len(DAZILIX_RECURRENT_LAYERS), s["heads"], s["gla_dim"], s["gla_vdim"], s["width"]
+    ffma_peak = 148 * 128 * 2 * peaks.get("sm_max_mhz", 1965.0) * 1e6
+
+    def ms_of(kernels: dict, name: str) -> float:
+        return kernels.get(name, {}).get("ms", 0.0)
+
+    ms = ms_of(m["prefill_kernels"], "gla_scan")
+    if ms > 0:
+        out["prefill_gla_scan_ms"] = round(ms, 3)
+        out["prefill_gla_scan_of_ffma_peak"] = round(L * 6.0 * PREFILL_TOKENS * H * d * e / (ms * 1e-3) / ffma_peak, 3)
+    ms = ms_of(m["prefill_kernels"], "branch_norm_add")
+    if ms > 0:
+        out["prefill_norms_of_hbm_peak"] = round(2 * s["layers"] * PREFILL_TOKENS * W * 12 / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)
+    for batch in DECODE_BATCHES:
+        ms = ms_of(m[f"decode_b{batch}_kernels"], "gla_scan")
+        if ms > 0:
+            out[f"decode_b{batch}_gla_scan_ms"] = round(ms, 4)
+            out[f"decode_b{batch}_gla_scan_of_hbm_peak"] = round(L * batch * H * d * e * 8 / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)
+    return out
+
+
+def _qwen3_norm_roofline(s: dict, m: dict, peaks: dict) -> dict[str, Any]:
+    ms = m["prefill_kernels"].get("add_rmsnorm", {}).get("ms", 0.0)
+    if ms <= 0:
+        return {}
+    # per layer two kernels that move the branch (bf16), the stream (float32, read and written) and the normed rows (bf16)
+    return {"prefill_norms_of_hbm_peak": round(2 * s["layers"] * PREFILL_TOKENS * s["width"] * 12 / (ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 3)}
+
+
+def run(steps: int, warmup: int, peaks: dict, which: str = "fegetar") -> dict[str, Any]:
     import gc
 
     import torch
@@ -174,14 +248,19 @@ def run(steps: int, warmup: int, peaks: dict) -> dict[str, Any]:
 
     result: dict[str, Any] = {"metric": "design_comparison", "dtype": "bf16", "data": "synthetic, random weights",
                               "prefill_tokens": PREFILL_TOKENS, "decode_context": DECODE_CONTEXT, "sizes": {}}
-    for name, s in SIZES.items():
+    sizes = DAZILIX_SIZES if which == "dazilix" else SIZES
+    for name, s in sizes.items():
         row: dict[str, Any] = {"size": s}
-        for design, cfg_dict in (("fegetar", fegetar_config(s)), ("qwen3", qwen3_config(s))):
+        pair = ((("dazilix", dazilix_config(s)), ("qwen3", qwen3_beside_dazilix(s))) if which == "dazilix" else
+                (("fegetar", fegetar_config(s)), ("qwen3", qwen3_config(s))))
+        for design, cfg_dict in pair:
             cfg = architecture_for(cfg_dict).config_from_dict(cfg_dict)
             model = random_model(cfg, seed=1, device="cuda", dtype="bfloat16", generate_on_device=True)
             m = _measure(model, steps, warmup)
             m["weight_bytes"] = model.weight_bytes()
             m.update(_attention_rooflines(design, s, m, peaks))
+            if which == "dazilix":
+                m.update(_dazilix_rooflines(s, m, peaks) if design == "dazilix" else _qwen3_norm_roofline(s, m, peaks))
             row[design] = m
             del model
             gc.collect()

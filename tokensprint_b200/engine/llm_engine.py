@@ -91,7 +91,8 @@ class LLMEngine:
             enforce_eager=config.enforce_eager,
             max_model_len=config.max_model_len,
         )
-        config.num_kvcache_blocks = self.model_runner.num_pages[0]
+        # (a model whose mixers keep fixed-size state only has no page pool at all)
+        config.num_kvcache_blocks = self.model_runner.num_pages[0] if self.model_runner.num_pages else 0
         self.model_runner.capture_graphs(config.max_num_seqs)  # nothing, if decode steps are not captured
         self.scheduler = Scheduler(config, self.model_runner.cache_manager)
         self.sampler = Sampler(model.device)

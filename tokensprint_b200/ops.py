@@ -1146,8 +1146,8 @@ def _attention_mma_fns(head_dim: int):
             raise KernelError(
                 f"attention_paged_mma: head_dim must be a multiple of 16 between 16 and {ATTENTION_MMA_MAX_HEAD_DIM}, got {head_dim}")
         lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim})
-        run = lib.ts_attention_paged_mma_fused
-        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+        run = lib.ts_attention_paged_mma_masked
+        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p]
         run.restype = _c_int
         scratch = lib.ts_attention_mma_scratch_floats
         scratch.argtypes = [_c_ll, _c_int]
@@ -1273,6 +1273,8 @@ def attention_paged_mma(
     scratch: Optional[torch.Tensor] = None,
     keys_per_split: int = 0,
     fuse_merge: bool = True,
+    chunk: int = 0,
+    sink: Optional[float] = None,
 ) -> None:
     """Causal attention over the paged cache on tensor cores (bfloat16).
 
@@ -1283,6 +1285,8 @@ def attention_paged_mma(
     keys_per_split > 0 (a multiple of 64) gives split s the keys [s * keys_per_split, ...),
     0 divides each sequence's keys evenly.  In decode steps the last CTA of each (sequence, KV
     head) pair merges the pair's splits itself (`fuse_merge`); otherwise a second kernel does.
+    chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from
+    position 0); sink: a score that joins every softmax's denominator without a value.
     """
     flush_gemm_chain()
     run, _ = _attention_mma_fns(head_dim)
@@ -1316,8 +1320,8 @@ def attention_paged_mma(
     _check("attention_paged_mma", run(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(scratch),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
-        block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits),
-        int(keys_per_split), counters, _stream()))
+        block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(chunk),
+        0 if sink is None else 1, 0.0 if sink is None else float(sink), int(splits), int(keys_per_split), counters, _stream()))
     if splits > 1:
         global launch_count
         launch_count += _attention_flat[d].ts_attention_mma_last_launches() - 1  # the combine kernel, if one ran

@@ -221,15 +221,15 @@ class AttentionMixer(Mixer):
 
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
-        plain_mask = self.chunk == 0 and self.sink is None
-        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d) and plain_mask:
+        plain_mask = self.chunk == 0 and self.sink is None  # the tcgen05 prompt kernel and the even-share decode kernel know no other
+        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
             B, singles = step.num_seqs, step.decode_seqs
             few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
             if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):
                 # few rows per sequence: the decode kernels, keys spread over CTAs
                 self._attend_decode(q, out, step, cache, tables, 0, B, step.max_seqlen_q)
                 return
-            prompts_on_tcgen05 = ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
+            prompts_on_tcgen05 = plain_mask and ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
             if prompts_on_tcgen05 and few_rows and 0 < singles < B:
                 # Single decoded tokens beside portions of prompts (the runner put the single tokens'
                 # requests first): each kind to its own kernel.  Through the prompt kernel a decoded
@@ -250,7 +250,7 @@ class AttentionMixer(Mixer):
             ops.attention_paged_mma(
                 q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
                 step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale,
-                self.window, 1, None, 0)
+                self.window, 1, None, 0, chunk=self.chunk, sink=self.sink)
             return
         # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
@@ -268,9 +268,10 @@ class AttentionMixer(Mixer):
         # The count must not depend on the step's actual lengths (a captured graph is
         # replayed for all of them): plan for a typical context, each sequence then
         # divides its own keys evenly.
-        context = ops.attention_decode_plan_context(step.max_context_len, self.window)
+        reach = min(self.window, self.chunk) if self.window and self.chunk else self.window or self.chunk  # the most keys a query sees
+        context = ops.attention_decode_plan_context(step.max_context_len, reach)
         splits = ops.attention_decode_splits(count, nkv, context, d)
-        if (ops.attention_decode_prefers_flat(count, nkv, splits, d)
+        if (self.chunk == 0 and self.sink is None and ops.attention_decode_prefers_flat(count, nkv, splits, d)
                 and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, count, max_q)):
             # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
             ops.attention_decode_flat(
@@ -282,7 +283,7 @@ class AttentionMixer(Mixer):
             scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d), device=q.device, dtype=torch.float32)
         ops.attention_paged_mma(
             q, cache.k_pages, cache.v_pages, out, cu, lens, table, seq_index, step.page_size, count, max_q, nq, nkv, d,
-            self.scale, self.window, splits, scratch, 0)
+            self.scale, self.window, splits, scratch, 0, chunk=self.chunk, sink=self.sink)
 
     # -- less common paths ----------------------------------------------------
 
