@@ -53,6 +53,11 @@ def _attend(kernel, q, k, v, positions, page, nq, nkv, d, scale, chunk, sink, dt
     qd = q.reshape(T, nq * d).to(dtype).to(DEV)
     if kernel == "simple":
         ops.attention_paged_simple(qd, kp, vp, out, pos, seq, table.view(1, -1).to(DEV), page, nq, nkv, d, scale, 0, chunk, sink)
+    elif kernel == "tcgen05":
+        cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+        lens = torch.tensor([positions[-1] + 1], dtype=torch.int32, device=DEV)
+        ops.attention_prefill_tcgen05(qd, kp, vp, out, cu, lens, table.view(1, -1).to(DEV), page, 1, T, nq, nkv, scale, 0, chunk=chunk, sink=sink)
+        ops.check_device_errors()
     else:
         cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
         lens = torch.tensor([positions[-1] + 1], dtype=torch.int32, device=DEV)
@@ -99,6 +104,26 @@ def test_block_attention_with_sink_random(kernel, dtype, nq, nkv, d, chunk, page
         positions = list(positions)
         got = _attend(kernel, q[positions], k[: positions[-1] + 1], v[: positions[-1] + 1], positions, page, nq, nkv, d, scale, chunk, 0.0, dtype)
         assert _rel(got, want[positions]) < TOL[dtype], (positions[0], positions[-1])
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+@pytest.mark.parametrize("nq, nkv, chunk, page", [(4, 2, 48, 16), (8, 1, 100, 16), (2, 2, 256, 64), (5, 1, 64, 8)])
+def test_block_attention_with_sink_heads_of_128(kernel, nq, nkv, chunk, page):
+    """Heads of 128, where prompt portions run on the tcgen05 kernel: portions of more rows than one
+    tile of 128 (two tiles per CTA) and of fewer, starting inside a block, with and without a sink."""
+    from tokensprint_b200 import ops
+
+    d, n, dtype = 128, 330, torch.bfloat16
+    if kernel == "tcgen05" and not ops.attention_tcgen05_supported(nq, nkv, d, page):
+        pytest.skip("sizes the tcgen05 kernel does not take")
+    q, k, v = (_randn(n, h, d, seed=s).to(dtype).double() for h, s in ((nq, 11), (nkv, 12), (nkv, 13)))
+    scale = 0.1
+    for sink in (0.0, None):
+        want = _plain_attend(q, k, v, range(n), nq, nkv, scale, chunk, sink is not None)
+        for positions in (range(n), range(chunk + 3, chunk + 3 + 21), range(2 * chunk - 7, n), range(5)):
+            positions = list(positions)
+            got = _attend(kernel, q[positions], k[: positions[-1] + 1], v[: positions[-1] + 1], positions, page, nq, nkv, d, scale, chunk, sink, dtype)
+            assert _rel(got, want[positions]) < TOL[dtype], (sink, positions[0], positions[-1])
 
 
 @pytest.mark.parametrize("kernel", KERNELS)

@@ -10,23 +10,28 @@
 // gla_scan: one CTA per (sequence, head, block of value columns).  A thread owns one value column
 // and d / R consecutive key channels of it in registers (R lanes of a warp share a column and add
 // their partial outputs by shuffles).  The CTA walks its sequence's tokens of the step in order,
-// GLA_TB at a time: q, k, the decay (worked out here, in float32, from z) and v of those tokens are
-// staged in shared memory by all threads, then every thread runs the GLA_TB updates from there.
+// up to GLA_TB at a time: q, k, the decay (worked out here, in float32, from z) and v of those tokens
+// are staged in shared memory by all threads, then every thread runs the round's updates from there.
 // The state is read from the request's slot before the first token and written back after the
 // last, so a sequence may be cut anywhere, and a token's result depends on nothing but its own
 // sequence: the same sums in the same order whatever else is in the batch.
 // A sequence without tokens in this step (a padded lane of a fixed-size batch) touches nothing.
 #include "common.cuh"
 
-#define GLA_TB 16        // tokens staged at a time, at most (fewer where d is so large that 16 do not fit 48 KB)
+#define GLA_TB 16        // tokens staged at a time, at most
 #define GLA_MAX_KP 32    // key channels per thread, at most
 #define GLA_THREADS 128
+#define GLA_PF 8         // staged q (k, z) entries a thread fetches ahead per round: tb * dp <= GLA_THREADS * GLA_PF
+#define GLA_PFV 4        // likewise for v: tb * cols <= GLA_THREADS * GLA_PFV
 
 __device__ __forceinline__ float gla_log_sigmoid(float z) {
   // log(1 / (1 + exp(-z))) without overflow on either side
   return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
+// The rounds are pipelined: while the threads run the updates of one round from shared memory, the
+// loads of the next round's q, k, z and v are in flight into registers (issued before the updates,
+// used after them), so the recurrence never waits for device memory.
 template <typename TA, int KP>
 __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const TA* __restrict__ z,
@@ -46,7 +51,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   if (t_end <= t_begin) return;
   const int r = threadIdx.x % R, cj = threadIdx.x / R;  // lanes of one column sit side by side
   const int col = col0 + cj;
-  const bool has_col = cj < cols_per_cta && col < e;
+  const bool has_col = col < e;
   const int c0 = r * KP;
   float* S = state + (((size_t)state_slots[b] * H + h) * d) * e;
   float s_reg[KP];
@@ -54,41 +59,77 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? S[(size_t)(c0 + i) * e + col] : 0.f;
 
   const size_t qk_off = (size_t)h * d, v_off = (size_t)h * e + col0;
-  for (int t0 = t_begin; t0 < t_end; t0 += tb) {
+  // what this thread fetches for a round: entries threadIdx.x + j * GLA_THREADS of the round's [tokens][dp] and [tokens][cols]
+  TA fq[GLA_PF], fk[GLA_PF], fz[GLA_PF], fv[GLA_PFV];
+  float fb[GLA_PF];  // the bias of the fetched channels (the same in every round only if dp divides the stride: fetched anew)
+  auto fetch = [&](int t0) {
     const int nt = min(tb, t_end - t0);
-    __syncthreads();  // the round before has been read
-    for (int i = threadIdx.x; i < nt * dp; i += GLA_THREADS) {
+#pragma unroll
+    for (int j = 0; j < GLA_PF; ++j) {
+      const int i = threadIdx.x + j * GLA_THREADS;
+      const int tt = i / dp, c = i - tt * dp;
+      if (i < nt * dp && c < d) {
+        const size_t at = (size_t)(t0 + tt) * ld_qkv + qk_off + c;
+        fq[j] = q[at];
+        fk[j] = k[at];
+        fz[j] = z[(size_t)(t0 + tt) * ld_z + qk_off + c];
+        fb[j] = bias ? bias[qk_off + c] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GLA_PFV; ++j) {
+      const int i = threadIdx.x + j * GLA_THREADS;
+      const int tt = i / cols_per_cta, c = i - tt * cols_per_cta;
+      if (i < nt * cols_per_cta && col0 + c < e) fv[j] = v[(size_t)(t0 + tt) * ld_qkv + v_off + c];
+    }
+  };
+  auto stage = [&](int t0) {  // the fetched entries into shared memory: q scaled, z turned into the decay, all float32
+    const int nt = min(tb, t_end - t0);
+#pragma unroll
+    for (int j = 0; j < GLA_PF; ++j) {
+      const int i = threadIdx.x + j * GLA_THREADS;
+      if (i >= nt * dp) continue;
       const int tt = i / dp, c = i - tt * dp;
       float qv = 0.f, kv = 0.f, av = 1.f;
       if (c < d) {
-        const size_t at = (size_t)(t0 + tt) * ld_qkv + qk_off + c;
-        qv = ts_to_float(q[at]) * q_scale;
-        kv = ts_to_float(k[at]);
-        const float zz = ts_to_float(z[(size_t)(t0 + tt) * ld_z + qk_off + c]) + (bias ? bias[qk_off + c] : 0.f);
-        av = expf(gla_log_sigmoid(zz) * inv_tau);
+        qv = ts_to_float(fq[j]) * q_scale;
+        kv = ts_to_float(fk[j]);
+        av = expf(gla_log_sigmoid(ts_to_float(fz[j]) + fb[j]) * inv_tau);
       }
       sq[i] = qv;
       sk[i] = kv;
       sa[i] = av;
     }
-    for (int i = threadIdx.x; i < nt * cols_per_cta; i += GLA_THREADS) {
-      const int tt = i / cols_per_cta, c = i - tt * cols_per_cta;
-      sv[i] = (col0 + c < e) ? ts_to_float(v[(size_t)(t0 + tt) * ld_qkv + v_off + c]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < GLA_PFV; ++j) {
+      const int i = threadIdx.x + j * GLA_THREADS;
+      if (i >= nt * cols_per_cta) continue;
+      const int c = i % cols_per_cta;
+      sv[i] = (col0 + c < e) ? ts_to_float(fv[j]) : 0.f;
     }
+  };
+
+  fetch(t_begin);
+  for (int t0 = t_begin; t0 < t_end; t0 += tb) {
+    const int nt = min(tb, t_end - t0);
+    __syncthreads();  // the round before has been read
+    stage(t0);
     __syncthreads();
+    if (t0 + tb < t_end) fetch(t0 + tb);  // in flight while this round's updates run
     for (int tt = 0; tt < nt; ++tt) {
-      const float vv = cj < cols_per_cta ? sv[tt * cols_per_cta + cj] : 0.f;
+      const float vv = sv[tt * cols_per_cta + cj];
       const float* pq = sq + tt * dp + c0;
       const float* pk = sk + tt * dp + c0;
       const float* pa = sa + tt * dp + c0;
-      float acc = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: the read-out is a sum of KP terms, its order is fixed by KP alone
 #pragma unroll
       for (int i = 0; i < KP; ++i) {
         s_reg[i] = fmaf(pa[i], s_reg[i], pk[i] * vv);
-        acc = fmaf(s_reg[i], pq[i], acc);
+        acc[i & 3] = fmaf(s_reg[i], pq[i], acc[i & 3]);
       }
-      for (int w = 1; w < R; w <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
-      if (r == 0 && has_col) o[((size_t)(t0 + tt) * H + h) * e + col] = acc;
+      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      for (int w = 1; w < R; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+      if (r == 0 && has_col) o[((size_t)(t0 + tt) * H + h) * e + col] = sum;
     }
   }
   if (has_col) {
@@ -102,11 +143,11 @@ template <typename TA, int KP>
 static int launch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, const float* bias,
                            float inv_tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H,
                            int d, int e, int R, cudaStream_t s) {
-  const int cols = GLA_THREADS / R;
-  const size_t per_token = (size_t)(3 * R * KP + cols) * sizeof(float);
-  const int tb = (int)min((size_t)GLA_TB, (size_t)(48 * 1024) / per_token);
+  const int cols = GLA_THREADS / R, dp = R * KP;
+  // tokens per round: what the threads' fetch registers hold, at most GLA_TB
+  const int tb = min(GLA_TB, min(GLA_THREADS * GLA_PF / dp, GLA_THREADS * GLA_PFV / cols));
   if (tb < 1) return TS_ERR_UNSUPPORTED_SIZE;
-  const size_t smem = tb * per_token;
+  const size_t smem = (size_t)tb * (3 * dp + cols) * sizeof(float);  // at most 16 * (3 * 64 + 128) or 1 * (3 * 1024 + 4) floats: below 48 KB
   const dim3 grid(B, H, (e + cols - 1) / cols);
   if (grid.y > 65535 || grid.z > 65535) return TS_ERR_UNSUPPORTED_SIZE;
   return ts_launch(gla_scan_kernel<TA, KP>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, (const TA*)z,
@@ -120,8 +161,11 @@ static int dispatch_gla_scan(const void* q, const void* k, const void* v, long l
   // R lanes per column, a power of two, so that a thread holds at most GLA_MAX_KP channels
   int R = 1;
   while (R < 32 && (d + R - 1) / R > GLA_MAX_KP) R <<= 1;
-  // fewer channels per thread where that fills the lanes better (decode: the state's bytes are the work)
-  while (R < 4 && (d + R - 1) / R > 8) R <<= 1;
+  // more lanes per column (fewer channels per thread, more CTAs) while the grid would leave SMs idle
+  // or a thread's chain of updates per token would be long; a function of the sizes and the batch alone
+  while (R < 32 && (d + R - 1) / R > 4 &&
+         ((d + R - 1) / R > 16 || (long long)B * H * ((e + GLA_THREADS / R - 1) / (GLA_THREADS / R)) < 2 * 148))
+    R <<= 1;
   const int kp = (d + R - 1) / R;
   if (kp > GLA_MAX_KP) return TS_ERR_UNSUPPORTED_SIZE;  // d > 1024
 #define GLA_CASE(KP) \

@@ -12,8 +12,14 @@
 // Sums of squares, the factor, the weights and the rotation are float32; one rounding at the store.
 //
 // One CTA per token.  A slot of -1 skips the stores into the cache; without `slot_mapping` keys and
-// values go to dense [T, nkv, d] buffers.
+// values go to dense [T, nkv, d] buffers.  The kernel right below reads the row from device memory
+// as it goes (rows too long for shared memory); the staged one after it is what normally runs.
 #include "common.cuh"
+
+__device__ __forceinline__ void ts_store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void ts_store_pair(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
 
 template <typename TA>
 __global__ void qk_joint_norm_rope_store_kernel(const TA* __restrict__ qk, long long ld, TA* __restrict__ q_out, TA* __restrict__ k_dst,
@@ -65,6 +71,87 @@ __global__ void qk_joint_norm_rope_store_kernel(const TA* __restrict__ qk, long 
   }
 }
 
+// The same through shared memory, for rows that fit it (every practical size): the row is read
+// once with the widest loads its alignment allows, partners of the rotation come from shared
+// memory, and q', k' and the values leave in pairs of elements.
+template <typename TA>
+__global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk, long long ld, TA* __restrict__ q_out, TA* __restrict__ k_dst,
+                                                       TA* __restrict__ v_dst, const int* __restrict__ slot_mapping,
+                                                       const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                                       const float* __restrict__ cos_sin, int rot, int nq, int nkv, int d, int wide) {
+  ts_pdl_prologue();
+  extern __shared__ float xs[];  // the row [q | k] as float32
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const TA* row = qk + (size_t)t * ld;
+  const int nQ = nq * d, nK = nkv * d, n = nQ + nK, half = rot >> 1;
+  float sq = 0.f, sk = 0.f;
+  if (wide) {  // n, nQ and ld are multiples of 4 and the row starts on a 4-element boundary
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+      float v[4];
+      if constexpr (sizeof(TA) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(row + i);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+      } else {
+        const float4 raw = *reinterpret_cast<const float4*>(row + i);
+        v[0] = raw.x, v[1] = raw.y, v[2] = raw.z, v[3] = raw.w;
+      }
+      const float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+      if (i < nQ) sq += ss; else sk += ss;
+      *reinterpret_cast<float4*>(xs + i) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = ts_to_float(row[i]);
+      if (i < nQ) sq += v * v; else sk += v * v;
+      xs[i] = v;
+    }
+  }
+  sq = ts_block_sum(sq, scratch);  // (its barriers also make the staged row visible to all threads)
+  sk = ts_block_sum(sk, scratch);
+  const float rq = 1.f / sqrtf(sq / (float)nQ + eps), rk = 1.f / sqrtf(sk / (float)nK + eps);
+  const float* cs = cos_sin + (size_t)t * half * 2;
+  const int slot = slot_mapping ? slot_mapping[t] : t;
+  auto element = [&](int i) -> float {  // entry i of [q' | k']
+    const bool is_q = i < nQ;
+    const int e = is_q ? i : i - nQ;
+    const float* w = is_q ? q_w : k_w;
+    const float r = is_q ? rq : rk;
+    const int j = e % d;
+    const float x = xs[i] * r * w[e];
+    if (j < half) return x * cs[2 * j] - xs[i + half] * r * w[e + half] * cs[2 * j + 1];
+    if (j < 2 * half) return x * cs[2 * (j - half)] + xs[i - half] * r * w[e - half] * cs[2 * (j - half) + 1];
+    return x;
+  };
+  TA* qd = q_out + (size_t)t * nQ;
+  const int stop = slot < 0 ? nQ : n;  // a token without a slot stores nothing of k
+  if ((d & 1) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_dst & 7) == 0 && ((uintptr_t)v_dst & 7) == 0) {
+    for (int i = threadIdx.x * 2; i < stop; i += blockDim.x * 2) {  // nQ and nK are even: a pair never straddles q and k
+      const float a = element(i), b = element(i + 1);
+      if (i < nQ) {
+        ts_store_pair(qd + i, a, b);
+      } else {
+        const size_t at = (size_t)slot * nK + (i - nQ);
+        ts_store_pair(k_dst + at, a, b);
+        ts_store_pair(v_dst + at, xs[i], xs[i + 1]);  // the rows were read from this element type: exact
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < stop; i += blockDim.x) {
+      const float a = element(i);
+      if (i < nQ) {
+        qd[i] = ts_from_float<TA>(a);
+      } else {
+        const size_t at = (size_t)slot * nK + (i - nQ);
+        k_dst[at] = ts_from_float<TA>(a);
+        v_dst[at] = ts_from_float<TA>(xs[i]);
+      }
+    }
+  }
+}
+
 TS_EXPORT int ts_qk_joint_norm_rope_store(const void* qk, int act_dtype, long long ld, void* q_out, void* k_dst, void* v_dst,
                                           const int* slot_mapping, const float* q_w, const float* k_w, float eps, const float* cos_sin,
                                           int rot, int T, int nq, int nkv, int d, void* stream) {
@@ -73,6 +160,20 @@ TS_EXPORT int ts_qk_joint_norm_rope_store(const void* qk, int act_dtype, long lo
   const int n = (nq + nkv) * d;
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
   cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = (size_t)n * sizeof(float);
+  if (smem <= 40 * 1024) {
+    const size_t elem = act_dtype == TS_DTYPE_F32 ? 4 : 2;
+    const int wide = (n % 4 == 0 && (nq * d) % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qk % (4 * elem)) == 0) ? 1 : 0;
+    const int th = wide ? min(512, max(64, (n / 4 + 31) / 32 * 32)) : threads;
+    if (act_dtype == TS_DTYPE_F32)
+      return ts_launch(qk_joint_norm_rope_store_staged_kernel<float>, dim3(T), dim3(th), smem, s, (const float*)qk, ld, (float*)q_out,
+                       (float*)k_dst, (float*)v_dst, slot_mapping, q_w, k_w, eps, cos_sin, rot, nq, nkv, d, wide);
+    if (act_dtype == TS_DTYPE_BF16)
+      return ts_launch(qk_joint_norm_rope_store_staged_kernel<__nv_bfloat16>, dim3(T), dim3(th), smem, s, (const __nv_bfloat16*)qk, ld,
+                       (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst, (__nv_bfloat16*)v_dst, slot_mapping, q_w, k_w, eps, cos_sin, rot, nq,
+                       nkv, d, wide);
+    return TS_ERR_BAD_ARGUMENT;
+  }
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(qk_joint_norm_rope_store_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)qk, ld, (float*)q_out,
                      (float*)k_dst, (float*)v_dst, slot_mapping, q_w, k_w, eps, cos_sin, rot, nq, nkv, d);

@@ -318,20 +318,94 @@ __global__ void branch_norm_add_kernel(const TB* __restrict__ branch, const floa
   }
 }
 
+// The same for widths that are a multiple of 4 (up to RN_MAX_CHUNKS * 4096): the branch row and the
+// stream's row stay in registers from the first sum of squares to the last store, every access is
+// 8 or 16 bytes wide and the loads are issued back to back.
+template <typename TB, typename TO>
+__global__ void branch_norm_add_vec_kernel(const TB* __restrict__ branch, const float* __restrict__ weight, const float* __restrict__ scale,
+                                           float* __restrict__ hidden, const float* __restrict__ next_weight, TO* __restrict__ out, int H,
+                                           float eps, float next_eps) {
+  ts_pdl_prologue();
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const TB* b = branch + (size_t)row * H;
+  float* h = hidden + (size_t)row * H;
+  const int chunks = H >> 2;
+  float4 bv[RN_MAX_CHUNKS], hv[RN_MAX_CHUNKS];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      bv[k] = ts_load4(b + 4 * c);
+      hv[k] = ts_load4(h + 4 * c);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) ss += bv[k].x * bv[k].x + bv[k].y * bv[k].y + bv[k].z * bv[k].z + bv[k].w * bv[k].w;
+  }
+  ss = ts_block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)H + eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      const float4 w = ts_load4(weight + 4 * c);
+      float4 add = make_float4(bv[k].x * rstd * w.x, bv[k].y * rstd * w.y, bv[k].z * rstd * w.z, bv[k].w * rstd * w.w);
+      if (scale) {
+        const float4 sc = ts_load4(scale + 4 * c);
+        add = make_float4(add.x * sc.x, add.y * sc.y, add.z * sc.z, add.w * sc.w);
+      }
+      hv[k] = make_float4(hv[k].x + add.x, hv[k].y + add.y, hv[k].z + add.z, hv[k].w + add.w);
+      ts_store4(h + 4 * c, hv[k]);
+      ss2 += hv[k].x * hv[k].x + hv[k].y * hv[k].y + hv[k].z * hv[k].z + hv[k].w * hv[k].w;
+    }
+  }
+  if (next_weight == nullptr) return;
+  ss2 = ts_block_sum(ss2, scratch);
+  const float rstd2 = 1.f / sqrtf(ss2 / (float)H + next_eps);
+#pragma unroll
+  for (int k = 0; k < RN_MAX_CHUNKS; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      const float4 w = ts_load4(next_weight + 4 * c);
+      ts_store4(out + (size_t)row * H + 4 * c, make_float4(hv[k].x * rstd2 * w.x, hv[k].y * rstd2 * w.y, hv[k].z * rstd2 * w.z, hv[k].w * rstd2 * w.w));
+    }
+  }
+}
+
+template <typename TB, typename TO>
+static int launch_branch_norm_add(const void* branch, const float* weight, const float* scale, float* hidden, const float* next_weight, void* out,
+                                  int rows, int H, float eps, float next_eps, cudaStream_t s) {
+  const int chunks = H >> 2;
+  const bool aligned = (H % 4 == 0) && (((uintptr_t)branch | (uintptr_t)weight | (uintptr_t)scale | (uintptr_t)hidden | (uintptr_t)next_weight |
+                                         (uintptr_t)out) % 16 == 0);
+  if (aligned && chunks <= RN_MAX_CHUNKS * 1024) {
+    int threads = (chunks + RN_MAX_CHUNKS - 1) / RN_MAX_CHUNKS;
+    if (rows <= 512) threads = chunks;  // few rows: one piece per thread, shortest latency
+    threads = min(1024, max(32, (threads + 31) / 32 * 32));
+    return ts_launch(branch_norm_add_vec_kernel<TB, TO>, dim3(rows), dim3(threads), 0, s, (const TB*)branch, weight, scale, hidden, next_weight,
+                     (TO*)out, H, eps, next_eps);
+  }
+  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
+  return ts_launch(branch_norm_add_kernel<TB, TO>, dim3(rows), dim3(threads), 0, s, (const TB*)branch, weight, scale, hidden, next_weight,
+                   (TO*)out, H, eps, next_eps);
+}
+
 TS_EXPORT int ts_branch_norm_add(const void* branch, int branch_dtype, const float* weight, const float* scale, float* hidden,
                                  const float* next_weight, void* out, int out_dtype, int rows, int H, float eps, float next_eps,
                                  void* stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || (next_weight != nullptr && out == nullptr)) return TS_ERR_BAD_ARGUMENT;
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
   if (next_weight == nullptr) out_dtype = branch_dtype;
   if (branch_dtype == TS_DTYPE_F32 && out_dtype == TS_DTYPE_F32)
-    return ts_launch(branch_norm_add_kernel<float, float>, dim3(rows), dim3(threads), 0, s, (const float*)branch, weight, scale, hidden,
-                     next_weight, (float*)out, H, eps, next_eps);
+    return launch_branch_norm_add<float, float>(branch, weight, scale, hidden, next_weight, out, rows, H, eps, next_eps, s);
   if (branch_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_BF16)
-    return ts_launch(branch_norm_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, s, (const __nv_bfloat16*)branch,
-                     weight, scale, hidden, next_weight, (__nv_bfloat16*)out, H, eps, next_eps);
+    return launch_branch_norm_add<__nv_bfloat16, __nv_bfloat16>(branch, weight, scale, hidden, next_weight, out, rows, H, eps, next_eps, s);
   return TS_ERR_BAD_ARGUMENT;
 }
 

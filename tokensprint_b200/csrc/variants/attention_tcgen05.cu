@@ -60,9 +60,19 @@ struct Params {
   const int* block_table; // [B, max_blocks]
   int* error;
   int max_blocks, page, nq, nkv, window, total_slots, num_seqs;
+  int chunk;        // > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from position 0)
+  int has_sink;     // 1: every softmax's denominator also holds exp(sink score): a key without a value
+  float sink_raw;   // the sink's score divided by the scale (the running max is kept in raw score units)
   float scale_log2;
   long long* probe;  // TS_ATT_PROBE builds: clock stamps of CTA 0's first softmax warp and of its MMA thread
 };
+
+// The first key a query at position `pos` sees: the start of its window, of its block of positions, or 0.
+__device__ __forceinline__ int first_visible_key(const Params& p, int pos) {
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos / p.chunk * p.chunk);
+  return lo;
+}
 
 #ifdef TS_ATT_PROBE
 #define PROBE(slot, blk, k) \
@@ -222,7 +232,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   const int last_row = min(r0 + RT, rows_total) - 1;
   const int hi = start_pos + last_row / G;          // last key any row of the tile sees
   const int first_pos = start_pos + r0 / G;         // position of the tile's first row
-  const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int lo = first_visible_key(p, first_pos);
   const int kb0 = lo / BN, kb1 = hi / BN;
   const int nblocks = kb1 - kb0 + 1;
   const int box_rows = min(p.page, BN);  // keys per copy: a whole page, or 64 keys of a larger one
@@ -316,11 +326,12 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   // Row state of this thread.
   const int r = r0 + tid;
   const int row_pos = (tid < RT && r < rows_total) ? start_pos + r / G : -1;
-  const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
+  const int row_lo = row_pos >= 0 ? first_visible_key(p, row_pos) : 0;
   float o[D];
 #pragma unroll
   for (int i = 0; i < D; ++i) o[i] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
+  // (with a sink the row's softmax starts from it: a key of a fixed score and no value)
+  float m_run = p.has_sink ? p.sink_raw : -INFINITY, l_run = p.has_sink ? 1.f : 0.f;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
   // A wait that gives up raises abort_s; the CTA leaves the loop together at the next barrier.
@@ -346,7 +357,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
 
     // every key of the block is seen by every row of the tile that belongs to a token (rows that belong
     // to nobody need no mask: a row's result depends on that row alone, and theirs is never stored)
-    const bool unmasked = (kbase + BN - 1 <= first_pos) && (p.window <= 0 || kbase >= start_pos + last_row / G - p.window + 1);
+    const bool unmasked = (kbase + BN - 1 <= first_pos) && kbase >= first_visible_key(p, start_pos + last_row / G);
     float m_new = m_run;
     if (unmasked) {
 #pragma unroll
@@ -599,7 +610,7 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
 
   // the last key any row of the pair sees, and how many key blocks the pair walks
   const int first_pos = start_pos + r0 / G;
-  const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int lo = first_visible_key(p, first_pos);
   const int kb0 = lo / PBN;
   const int hi = start_pos + (min(r0 + ntiles * RT, rows_total) - 1) / G;
   // Both tiles walk all blocks of the later one (its last block may be fully masked for the
@@ -797,14 +808,16 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
     const int row = quad * 32 + lane;
     const int r = r0 + t * RT + row;
     const int row_pos = (row < RT && r < rows_total) ? start_pos + r / G : -1;
-    const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
+    const int row_lo = row_pos >= 0 ? first_visible_key(p, row_pos) : 0;
     const int tile_first_pos = start_pos + (r0 + t * RT) / G;
     const int tile_last_pos = start_pos + (min(r0 + t * RT + RT, rows_total) - 1) / G;  // of the tile's rows that belong to a token
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t s_addr = lane_addr + t * 128 + h * 64;        // this thread's 64 scores; its P goes over the first 32 of them
     const int pair_bar = 3 + t * 4 + quad;                       // hardware barrier of the two warps that share rows
     const uint32_t o_addr = lane_addr + 256 + t * 128 + h * 64;  // its half of the row of O
-    float m_run = -INFINITY, l_run = 0.f;  // l_run: the sum over this thread's keys only
+    // l_run: the sum over this thread's keys only; with a sink both threads of a row start from its score
+    // and one of them holds its share of the sum
+    float m_run = p.has_sink ? p.sink_raw : -INFINITY, l_run = (p.has_sink && h == 0) ? 1.f : 0.f;
     bool ok = true;
 
     for (int blk = 0; blk < nblocks; ++blk) {
@@ -816,7 +829,7 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // every one of these 64 keys is seen by every row of the tile that belongs to a token (rows that
       // belong to nobody need no mask: a row's result depends on that row alone, and theirs is never stored)
-      const bool unmasked = (kbase + 63 <= tile_first_pos) && (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
+      const bool unmasked = (kbase + 63 <= tile_first_pos) && kbase >= first_visible_key(p, tile_last_pos);
       // First walk over this thread's 64 scores: their largest.
       float m_blk;
       {
@@ -1053,8 +1066,10 @@ TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
 TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, const void* vcache, void* out,
                                            const int* cu_q, const int* ctx_len, const int* block_table,
                                            int max_blocks, int page, long long total_slots, int T, int B, int max_q,
-                                           int nq, int nkv, float scale, int window, int mode, int* error, void* stream_) {
+                                           int nq, int nkv, float scale, int window, int chunk, int has_sink, float sink_score,
+                                           int mode, int* error, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
+  if (chunk < 0 || (has_sink && !(scale > 0.f))) return TS_ERR_BAD_ARGUMENT;
   if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
     return TS_ERR_BAD_ARGUMENT;
   if (total_slots > 0x7fffffffLL - page || ((long long)max_q * (nq / nkv) / ((BM / (nq / nkv)) * (nq / nkv)) + 1) * nkv * B > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
@@ -1070,6 +1085,9 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   p.nq = nq;
   p.nkv = nkv;
   p.window = window;
+  p.chunk = chunk;
+  p.has_sink = has_sink ? 1 : 0;
+  p.sink_raw = has_sink ? sink_score / scale : 0.f;
   p.total_slots = (int)total_slots;
   p.num_seqs = B;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -1452,7 +1452,7 @@ def _attention_tcgen05_fns():
     if _attention_tcgen05 is None:
         lib = _build.load_variant("attention_tcgen05", {"TS_HEAD_DIM": ATTENTION_TCGEN05_HEAD_DIM})
         run = lib.ts_attention_prefill_tcgen05
-        run.argtypes = [_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_int, _c_void_p, _c_void_p]
+        run.argtypes = [_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p]
         run.restype = _c_int
         ok = lib.ts_attention_tcgen05_supported
         ok.argtypes = [_c_int, _c_int, _c_int]
@@ -1488,6 +1488,8 @@ def attention_prefill_tcgen05(
     scale: float,
     window: int = 0,
     mode: int = 0,
+    chunk: int = 0,
+    sink: Optional[float] = None,
 ) -> None:
     """Causal attention of prompt portions over the paged cache, tcgen05 tensor cores, head size 128.
 
@@ -1521,7 +1523,8 @@ def attention_prefill_tcgen05(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, k_cache.shape[0] * page_size, T, num_seqs, max_seqlen_q, nq, nkv,
-        float(scale), int(window), int(mode), error.data_ptr(), _stream()))
+        float(scale), int(window), int(chunk), 0 if sink is None else 1, 0.0 if sink is None else float(sink), int(mode),
+        error.data_ptr(), _stream()))
 
 
 # ---------------------------------------------------------------------------

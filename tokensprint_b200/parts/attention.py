@@ -221,7 +221,6 @@ class AttentionMixer(Mixer):
 
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
-        plain_mask = self.chunk == 0 and self.sink is None  # the tcgen05 prompt kernel and the even-share decode kernel know no other
         if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
             B, singles = step.num_seqs, step.decode_seqs
             few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
@@ -229,7 +228,7 @@ class AttentionMixer(Mixer):
                 # few rows per sequence: the decode kernels, keys spread over CTAs
                 self._attend_decode(q, out, step, cache, tables, 0, B, step.max_seqlen_q)
                 return
-            prompts_on_tcgen05 = plain_mask and ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
+            prompts_on_tcgen05 = ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
             if prompts_on_tcgen05 and few_rows and 0 < singles < B:
                 # Single decoded tokens beside portions of prompts (the runner put the single tokens'
                 # requests first): each kind to its own kernel.  Through the prompt kernel a decoded
@@ -239,13 +238,14 @@ class AttentionMixer(Mixer):
                 self._attend_decode(q[:singles], out[:singles], step, cache, tables, 0, singles, 1)
                 ops.attention_prefill_tcgen05(
                     q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q[singles:], step.context_lens[singles:],
-                    tables.block_table[singles:], step.page_size, B - singles, step.max_seqlen_q, nq, nkv, self.scale, self.window)
+                    tables.block_table[singles:], step.page_size, B - singles, step.max_seqlen_q, nq, nkv, self.scale, self.window,
+                    chunk=self.chunk, sink=self.sink)
                 return
             if prompts_on_tcgen05:
                 # prompt portions: the tcgen05 kernel, where it takes the sizes
                 ops.attention_prefill_tcgen05(
                     q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
-                    step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, self.scale, self.window)
+                    step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, self.scale, self.window, chunk=self.chunk, sink=self.sink)
                 return
             ops.attention_paged_mma(
                 q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
@@ -271,6 +271,7 @@ class AttentionMixer(Mixer):
         reach = min(self.window, self.chunk) if self.window and self.chunk else self.window or self.chunk  # the most keys a query sees
         context = ops.attention_decode_plan_context(step.max_context_len, reach)
         splits = ops.attention_decode_splits(count, nkv, context, d)
+        # (the even-share decode kernel knows neither a block bound nor a sink)
         if (self.chunk == 0 and self.sink is None and ops.attention_decode_prefers_flat(count, nkv, splits, d)
                 and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, count, max_q)):
             # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
