@@ -120,7 +120,7 @@ def test_block_attention_with_sink_heads_of_128(kernel, nq, nkv, chunk, page):
     scale = 0.1
     for sink in (0.0, None):
         want = _plain_attend(q, k, v, range(n), nq, nkv, scale, chunk, sink is not None)
-        for positions in (range(n), range(chunk + 3, chunk + 3 + 21), range(2 * chunk - 7, n), range(5)):
+        for positions in (range(n), range(chunk + 3, chunk + 3 + 21), range(min(2 * chunk, n - 30) - 7, n), range(5)):
             positions = list(positions)
             got = _attend(kernel, q[positions], k[: positions[-1] + 1], v[: positions[-1] + 1], positions, page, nq, nkv, d, scale, chunk, sink, dtype)
             assert _rel(got, want[positions]) < TOL[dtype], (sink, positions[0], positions[-1])

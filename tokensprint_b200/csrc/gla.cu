@@ -7,11 +7,14 @@
 //   o_t = S_t^T (q_t * q_scale)
 // then  out_t = o_t * rsqrt(mean_e(o_t^2) + eps) * w_norm * silu(g_t)   per head (gla_norm_gate).
 //
+// gla_decay: the decays of all tokens and channels once, float32 (every CTA of the scan that shares a
+// head reads them; worked out inside the scan they were computed once per block of value columns).
+//
 // gla_scan: one CTA per (sequence, head, block of value columns).  A thread owns one value column
 // and d / R consecutive key channels of it in registers (R lanes of a warp share a column and add
 // their partial outputs by shuffles).  The CTA walks its sequence's tokens of the step in order,
-// up to GLA_TB at a time: q, k, the decay (worked out here, in float32, from z) and v of those tokens
-// are staged in shared memory by all threads, then every thread runs the round's updates from there.
+// up to GLA_TB at a time: q, k, the decay and v of those tokens are staged in shared memory by all
+// threads, then every thread runs the round's updates from there.
 // The state is read from the request's slot before the first token and written back after the
 // last, so a sequence may be cut anywhere, and a token's result depends on nothing but its own
 // sequence: the same sums in the same order whatever else is in the batch.
@@ -29,17 +32,30 @@ __device__ __forceinline__ float gla_log_sigmoid(float z) {
   return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
+// Loads that stay where they are written: the compiler otherwise moves a load whose value is first
+// used after the round's updates down to that use, and the round then waits for device memory once
+// per entry instead of never.
+__device__ __forceinline__ float gla_load(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ __nv_bfloat16 gla_load(const __nv_bfloat16* p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return __ushort_as_bfloat16(v);
+}
+
 // The rounds are pipelined: while the threads run the updates of one round from shared memory, the
 // loads of the next round's q, k, z and v are in flight into registers (issued before the updates,
 // used after them), so the recurrence never waits for device memory.
 template <typename TA, int KP>
 __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
-    const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const TA* __restrict__ z,
-    long long ld_z, const float* __restrict__ bias, float inv_tau, float q_scale, float* __restrict__ state,
-    const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens, float* __restrict__ o, int H, int d, int e, int R,
-    int cols_per_cta, int tb) {
+    const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const float* __restrict__ decay,
+    float q_scale, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
+    float* __restrict__ o, int H, int d, int e, int R, int cols_per_cta, int tb) {
   ts_pdl_prologue();
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   // staged per token: q, k, decay [dp] each, v [cols]
   const int dp = R * KP;  // d padded to the channels the threads cover
   float* sq = sm;
@@ -60,52 +76,58 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
 
   const size_t qk_off = (size_t)h * d, v_off = (size_t)h * e + col0;
   // what this thread fetches for a round: entries threadIdx.x + j * GLA_THREADS of the round's [tokens][dp] and [tokens][cols]
-  TA fq[GLA_PF], fk[GLA_PF], fz[GLA_PF], fv[GLA_PFV];
-  float fb[GLA_PF];  // the bias of the fetched channels (the same in every round only if dp divides the stride: fetched anew)
+  TA fq[GLA_PF], fk[GLA_PF], fv[GLA_PFV];
+  float fa[GLA_PF];
+  // Entry i of a round is channel i % dp of token i / dp (for v: column i % cols of token i / cols); a thread's
+  // entries lie GLA_THREADS apart, so their places are found once, by steps, without a division per entry.
+  const int Hd = H * d;
+  const int step_t = GLA_THREADS / dp, step_c = GLA_THREADS % dp, first_t = (int)threadIdx.x / dp, first_c = (int)threadIdx.x % dp;
+  const int vstep_t = GLA_THREADS / cols_per_cta, vstep_c = GLA_THREADS % cols_per_cta;
+  const int vfirst_t = (int)threadIdx.x / cols_per_cta, vfirst_c = (int)threadIdx.x % cols_per_cta;
   auto fetch = [&](int t0) {
     const int nt = min(tb, t_end - t0);
+    int tt = first_t, c = first_c;
 #pragma unroll
     for (int j = 0; j < GLA_PF; ++j) {
-      const int i = threadIdx.x + j * GLA_THREADS;
-      const int tt = i / dp, c = i - tt * dp;
-      if (i < nt * dp && c < d) {
-        const size_t at = (size_t)(t0 + tt) * ld_qkv + qk_off + c;
-        fq[j] = q[at];
-        fk[j] = k[at];
-        fz[j] = z[(size_t)(t0 + tt) * ld_z + qk_off + c];
-        fb[j] = bias ? bias[qk_off + c] : 0.f;
+      {  // an entry beyond the round's tokens or the head's channels reads a valid place and is not used
+        const int tr = t0 + min(tt, nt - 1), cr = min(c, d - 1);
+        const size_t at = (size_t)tr * ld_qkv + qk_off + cr;
+        fq[j] = gla_load(q + at);
+        fk[j] = gla_load(k + at);
+        fa[j] = gla_load(decay + (size_t)tr * Hd + qk_off + cr);
       }
+      tt += step_t, c += step_c;
+      if (c >= dp) c -= dp, ++tt;
     }
+    tt = vfirst_t, c = vfirst_c;
 #pragma unroll
     for (int j = 0; j < GLA_PFV; ++j) {
-      const int i = threadIdx.x + j * GLA_THREADS;
-      const int tt = i / cols_per_cta, c = i - tt * cols_per_cta;
-      if (i < nt * cols_per_cta && col0 + c < e) fv[j] = v[(size_t)(t0 + tt) * ld_qkv + v_off + c];
+      fv[j] = gla_load(v + (size_t)(t0 + min(tt, nt - 1)) * ld_qkv + v_off + min(c, e - 1 - col0));
+      tt += vstep_t, c += vstep_c;
+      if (c >= cols_per_cta) c -= cols_per_cta, ++tt;
     }
   };
-  auto stage = [&](int t0) {  // the fetched entries into shared memory: q scaled, z turned into the decay, all float32
+  auto stage = [&](int t0) {  // the fetched entries into shared memory as float32, q scaled
     const int nt = min(tb, t_end - t0);
+    int tt = first_t, c = first_c;
 #pragma unroll
     for (int j = 0; j < GLA_PF; ++j) {
-      const int i = threadIdx.x + j * GLA_THREADS;
-      if (i >= nt * dp) continue;
-      const int tt = i / dp, c = i - tt * dp;
-      float qv = 0.f, kv = 0.f, av = 1.f;
-      if (c < d) {
-        qv = ts_to_float(fq[j]) * q_scale;
-        kv = ts_to_float(fk[j]);
-        av = expf(gla_log_sigmoid(ts_to_float(fz[j]) + fb[j]) * inv_tau);
+      if (tt < nt) {
+        const bool real = c < d;
+        const int i = tt * dp + c;
+        sq[i] = real ? ts_to_float(fq[j]) * q_scale : 0.f;
+        sk[i] = real ? ts_to_float(fk[j]) : 0.f;
+        sa[i] = real ? fa[j] : 1.f;
       }
-      sq[i] = qv;
-      sk[i] = kv;
-      sa[i] = av;
+      tt += step_t, c += step_c;
+      if (c >= dp) c -= dp, ++tt;
     }
+    tt = vfirst_t, c = vfirst_c;
 #pragma unroll
     for (int j = 0; j < GLA_PFV; ++j) {
-      const int i = threadIdx.x + j * GLA_THREADS;
-      if (i >= nt * cols_per_cta) continue;
-      const int c = i % cols_per_cta;
-      sv[i] = (col0 + c < e) ? ts_to_float(fv[j]) : 0.f;
+      if (tt < nt) sv[tt * cols_per_cta + c] = (col0 + c < e) ? ts_to_float(fv[j]) : 0.f;
+      tt += vstep_t, c += vstep_c;
+      if (c >= cols_per_cta) c -= cols_per_cta, ++tt;
     }
   };
 
@@ -116,16 +138,25 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     stage(t0);
     __syncthreads();
     if (t0 + tb < t_end) fetch(t0 + tb);  // in flight while this round's updates run
+#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = sv[tt * cols_per_cta + cj];
-      const float* pq = sq + tt * dp + c0;
-      const float* pk = sk + tt * dp + c0;
-      const float* pa = sa + tt * dp + c0;
+      // a thread's KP channels are a multiple of four and start on a 16-byte boundary: 16-byte loads
+      const float4* pq = reinterpret_cast<const float4*>(sq + tt * dp + c0);
+      const float4* pk = reinterpret_cast<const float4*>(sk + tt * dp + c0);
+      const float4* pa = reinterpret_cast<const float4*>(sa + tt * dp + c0);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: the read-out is a sum of KP terms, its order is fixed by KP alone
 #pragma unroll
-      for (int i = 0; i < KP; ++i) {
-        s_reg[i] = fmaf(pa[i], s_reg[i], pk[i] * vv);
-        acc[i & 3] = fmaf(s_reg[i], pq[i], acc[i & 3]);
+      for (int i = 0; i < KP / 4; ++i) {
+        const float4 a4 = pa[i], k4 = pk[i], q4 = pq[i];
+        s_reg[4 * i + 0] = fmaf(a4.x, s_reg[4 * i + 0], k4.x * vv);
+        s_reg[4 * i + 1] = fmaf(a4.y, s_reg[4 * i + 1], k4.y * vv);
+        s_reg[4 * i + 2] = fmaf(a4.z, s_reg[4 * i + 2], k4.z * vv);
+        s_reg[4 * i + 3] = fmaf(a4.w, s_reg[4 * i + 3], k4.w * vv);
+        acc[0] = fmaf(s_reg[4 * i + 0], q4.x, acc[0]);
+        acc[1] = fmaf(s_reg[4 * i + 1], q4.y, acc[1]);
+        acc[2] = fmaf(s_reg[4 * i + 2], q4.z, acc[2]);
+        acc[3] = fmaf(s_reg[4 * i + 3], q4.w, acc[3]);
       }
       float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
       for (int w = 1; w < R; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
@@ -140,9 +171,8 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
 }
 
 template <typename TA, int KP>
-static int launch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, const float* bias,
-                           float inv_tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H,
-                           int d, int e, int R, cudaStream_t s) {
+static int launch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
+                           const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int R, cudaStream_t s) {
   const int cols = GLA_THREADS / R, dp = R * KP;
   // tokens per round: what the threads' fetch registers hold, at most GLA_TB
   const int tb = min(GLA_TB, min(GLA_THREADS * GLA_PF / dp, GLA_THREADS * GLA_PFV / cols));
@@ -150,14 +180,13 @@ static int launch_gla_scan(const void* q, const void* k, const void* v, long lon
   const size_t smem = (size_t)tb * (3 * dp + cols) * sizeof(float);  // at most 16 * (3 * 64 + 128) or 1 * (3 * 1024 + 4) floats: below 48 KB
   const dim3 grid(B, H, (e + cols - 1) / cols);
   if (grid.y > 65535 || grid.z > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(gla_scan_kernel<TA, KP>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, (const TA*)z,
-                   ld_z, bias, inv_tau, q_scale, state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb);
+  return ts_launch(gla_scan_kernel<TA, KP>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, decay, q_scale,
+                   state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb);
 }
 
 template <typename TA>
-static int dispatch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, const float* bias,
-                             float inv_tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H,
-                             int d, int e, cudaStream_t s) {
+static int dispatch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
+                             const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, cudaStream_t s) {
   // R lanes per column, a power of two, so that a thread holds at most GLA_MAX_KP channels
   int R = 1;
   while (R < 32 && (d + R - 1) / R > GLA_MAX_KP) R <<= 1;
@@ -166,10 +195,15 @@ static int dispatch_gla_scan(const void* q, const void* k, const void* v, long l
   while (R < 32 && (d + R - 1) / R > 4 &&
          ((d + R - 1) / R > 16 || (long long)B * H * ((e + GLA_THREADS / R - 1) / (GLA_THREADS / R)) < 2 * 148))
     R <<= 1;
+  if (const char* forced = getenv("TS_GLA_LANES")) {  // for measurements: a fixed number of lanes per column
+    const int want = atoi(forced);
+    if (want >= 1 && want <= 32 && (want & (want - 1)) == 0 && (d + want - 1) / want <= GLA_MAX_KP) R = want;
+  }
   const int kp = (d + R - 1) / R;
   if (kp > GLA_MAX_KP) return TS_ERR_UNSUPPORTED_SIZE;  // d > 1024
+  static_assert(GLA_MAX_KP % 4 == 0, "a thread's channels come in fours");
 #define GLA_CASE(KP) \
-  if (kp <= KP) return launch_gla_scan<TA, KP>(q, k, v, ld_qkv, z, ld_z, bias, inv_tau, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, s)
+  if (kp <= KP) return launch_gla_scan<TA, KP>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, s)
   GLA_CASE(4);
   GLA_CASE(8);
   GLA_CASE(12);
@@ -180,20 +214,46 @@ static int dispatch_gla_scan(const void* q, const void* k, const void* v, long l
   return TS_ERR_UNSUPPORTED_SIZE;
 }
 
+// decay[t, c] = sigmoid(z[t, c] + bias[c])^(1/tau) = exp(logsigmoid(z + bias) / tau), float32, for all H*d channels c.
+template <typename TA>
+__global__ void gla_decay_kernel(const TA* __restrict__ z, long long ld_z, const float* __restrict__ bias, float inv_tau,
+                                 float* __restrict__ decay, int T, int n) {
+  ts_pdl_prologue();
+  const int t = blockIdx.y;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n; c += gridDim.x * blockDim.x) {
+    const float zz = ts_to_float(z[(size_t)t * ld_z + c]) + (bias ? bias[c] : 0.f);
+    decay[(size_t)t * n + c] = expf(gla_log_sigmoid(zz) * inv_tau);
+  }
+}
+
+// z [T, H*d] with row stride ld_z; bias [H*d] float32 or null; decay [T, H*d] float32.
+TS_EXPORT int ts_gla_decay(const void* z, long long ld_z, int act_dtype, const float* bias, float tau, float* decay, int T, int n,
+                           void* stream) {
+  if (T <= 0) return 0;
+  if (n <= 0 || !(tau > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  if (T > 65535 * 64) return TS_ERR_UNSUPPORTED_SIZE;
+  // rows in the grid's y; beyond 65,535 rows a block takes several (a row index is then folded into the channel index)
+  cudaStream_t s = (cudaStream_t)stream;
+  const dim3 grid((n + 255) / 256, T);
+  if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  if (act_dtype == TS_DTYPE_F32)
+    return ts_launch(gla_decay_kernel<float>, grid, dim3(256), 0, s, (const float*)z, ld_z, bias, 1.f / tau, decay, T, n);
+  if (act_dtype == TS_DTYPE_BF16)
+    return ts_launch(gla_decay_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)z, ld_z, bias, 1.f / tau, decay, T, n);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
 // q, k [T, H*d] and v [T, H*e] are views with the common row stride ld_qkv (columns of one product's
-// result); z [T, H*d] with row stride ld_z; bias [H*d] float32; state [slots, H, d, e] float32;
-// o [T, H*e] float32.
-TS_EXPORT int ts_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const void* z, long long ld_z, int act_dtype,
-                          const float* bias, float tau, float q_scale, float* state, const int* state_slots, const int* cu_seqlens,
-                          float* o, int B, int H, int d, int e, void* stream) {
+// result); decay [T, H*d] float32 (gla_decay); state [slots, H, d, e] float32; o [T, H*e] float32.
+TS_EXPORT int ts_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, int act_dtype, const float* decay, float q_scale,
+                          float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, void* stream) {
   if (B <= 0) return 0;
-  if (H <= 0 || d <= 0 || e <= 0 || !(tau > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  if (H <= 0 || d <= 0 || e <= 0) return TS_ERR_BAD_ARGUMENT;
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    return dispatch_gla_scan<float>(q, k, v, ld_qkv, z, ld_z, bias, 1.f / tau, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, s);
+    return dispatch_gla_scan<float>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, s);
   if (act_dtype == TS_DTYPE_BF16)
-    return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, z, ld_z, bias, 1.f / tau, q_scale, state, state_slots, cu_seqlens, o, B, H, d,
-                                            e, s);
+    return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, s);
   return TS_ERR_BAD_ARGUMENT;
 }
 

@@ -81,7 +81,7 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
                                                        const float* __restrict__ cos_sin, int rot, int nq, int nkv, int d, int wide) {
   ts_pdl_prologue();
   extern __shared__ float xs[];  // the row [q | k] as float32
-  __shared__ float scratch[33];
+  __shared__ float2 scratch2[33];
   const int t = blockIdx.x;
   const TA* row = qk + (size_t)t * ld;
   const int nQ = nq * d, nK = nkv * d, n = nQ + nK, half = rot >> 1;
@@ -109,17 +109,30 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
       xs[i] = v;
     }
   }
-  sq = ts_block_sum(sq, scratch);  // (its barriers also make the staged row visible to all threads)
-  sk = ts_block_sum(sk, scratch);
+  {  // both sums of squares in one pass over the block (its barriers also make the staged row visible to all threads)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    sq = ts_warp_sum(sq);
+    sk = ts_warp_sum(sk);
+    if (lane == 0) scratch2[warp] = make_float2(sq, sk);
+    __syncthreads();
+    if (warp == 0) {
+      float2 v = lane < nwarps ? scratch2[lane] : make_float2(0.f, 0.f);
+      v.x = ts_warp_sum(v.x);
+      v.y = ts_warp_sum(v.y);
+      if (lane == 0) scratch2[32] = v;
+    }
+    __syncthreads();
+    sq = scratch2[32].x;
+    sk = scratch2[32].y;
+  }
   const float rq = 1.f / sqrtf(sq / (float)nQ + eps), rk = 1.f / sqrtf(sk / (float)nK + eps);
   const float* cs = cos_sin + (size_t)t * half * 2;
   const int slot = slot_mapping ? slot_mapping[t] : t;
-  auto element = [&](int i) -> float {  // entry i of [q' | k']
+  auto element = [&](int i, int j) -> float {  // entry i of [q' | k'], which is entry j of its head
     const bool is_q = i < nQ;
     const int e = is_q ? i : i - nQ;
     const float* w = is_q ? q_w : k_w;
     const float r = is_q ? rq : rk;
-    const int j = e % d;
     const float x = xs[i] * r * w[e];
     if (j < half) return x * cs[2 * j] - xs[i + half] * r * w[e + half] * cs[2 * j + 1];
     if (j < 2 * half) return x * cs[2 * (j - half)] + xs[i - half] * r * w[e - half] * cs[2 * (j - half) + 1];
@@ -128,8 +141,13 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
   TA* qd = q_out + (size_t)t * nQ;
   const int stop = slot < 0 ? nQ : n;  // a token without a slot stores nothing of k
   if ((d & 1) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_dst & 7) == 0 && ((uintptr_t)v_dst & 7) == 0) {
-    for (int i = threadIdx.x * 2; i < stop; i += blockDim.x * 2) {  // nQ and nK are even: a pair never straddles q and k
-      const float a = element(i), b = element(i + 1);
+    // a thread's place inside a head moves by the same amount every round: no division in the loop
+    const int step = (blockDim.x * 2) % d;
+    int j = (threadIdx.x * 2) % d;
+    for (int i = threadIdx.x * 2; i < stop; i += blockDim.x * 2) {  // nQ and nK are even: a pair never straddles q and k, nor two heads
+      const float a = element(i, j), b = element(i + 1, j + 1);
+      j += step;
+      if (j >= d) j -= d;
       if (i < nQ) {
         ts_store_pair(qd + i, a, b);
       } else {
@@ -140,7 +158,7 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
     }
   } else {
     for (int i = threadIdx.x; i < stop; i += blockDim.x) {
-      const float a = element(i);
+      const float a = element(i, i % d);
       if (i < nQ) {
         qd[i] = ts_from_float<TA>(a);
       } else {

@@ -178,7 +178,7 @@ def _attention_rooflines(design: str, s: dict, m: dict, peaks: dict) -> dict[str
         row_bytes = 576 * 2
     elif design == "dazilix":
         L = s["layers"] - len(DAZILIX_RECURRENT_LAYERS)
-        names = ("attention_paged_mma",)
+        names = ("attention_prefill_tcgen05", "attention_paged_mma")
         flops = L * 4 * H * 128 * pairs
         row_bytes = 2 * 8 * 128 * 2
     else:

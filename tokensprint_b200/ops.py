@@ -62,8 +62,9 @@ _SIGNATURES = {
     "ts_moe_down": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_qk_joint_norm_rope_store": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float,
                                     _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "ts_gla_scan": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_ll, _c_int, _c_void_p, _c_float, _c_float, _c_void_p, _c_void_p,
-                    _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_gla_decay": [_c_void_p, _c_ll, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_void_p],
+    "ts_gla_scan": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                    _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_gla_norm_gate": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "ts_branch_norm_add": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float,
                            _c_void_p],
@@ -659,7 +660,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     q, k [T, H*d] and v [T, H*e]: views with one common row stride (columns of one product's result);
     z [T, H*d] with its own; bias [H*d] float32 or None; state [slots, H, d, e] float32, read at a
     sequence's slot before its first token of the step and written after its last; state_slots [B],
-    cu_seqlens [B+1] int32; out [T, H*e] float32.  Everything but the loads is float32."""
+    cu_seqlens [B+1] int32; out [T, H*e] float32.  Everything but the loads is float32.  Two launches:
+    the decays of all tokens and channels once (float32 scratch [T, H*d]), then the recurrence."""
     flush_gemm_chain()
     H, d, e = int(num_heads), int(key_dim), int(value_dim)
     if d > GLA_MAX_KEY_DIM:
@@ -682,9 +684,12 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         _cuda_contig("bias", bias, torch.float32)
         if bias.numel() != H * d:
             raise KernelError("gla_scan: the bias must have one entry per key channel")
+    decay = torch.empty((T, H * d), device=q.device, dtype=torch.float32)
+    code, stream = _act_code("q", q), _stream()
+    _check("gla_scan", _fn("ts_gla_decay")(z.data_ptr(), z.stride(0), code, _ptr(bias), float(tau), decay.data_ptr(), T, H * d, stream))
     _check("gla_scan", _fn("ts_gla_scan")(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), z.data_ptr(), z.stride(0), _act_code("q", q), _ptr(bias), float(tau),
-        float(q_scale), state.data_ptr(), state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, d, e, _stream()))
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), code, decay.data_ptr(), float(q_scale), state.data_ptr(),
+        state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, d, e, stream))
 
 
 def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_heads: int, value_dim: int, eps: float) -> None:
