@@ -400,9 +400,9 @@ def test_decoded_tokens_beside_portions_go_to_their_own_kernels(folder, monkeypa
     calls = []
     prompt_kernel = ops.attention_prefill_tcgen05
 
-    def spy(q, k, v, out, cu, lens, table, page, num_seqs, max_q, *rest):
+    def spy(q, k, v, out, cu, lens, table, page, num_seqs, max_q, *rest, **options):
         calls.append((int(num_seqs), int(max_q), q.shape[0]))
-        return prompt_kernel(q, k, v, out, cu, lens, table, page, num_seqs, max_q, *rest)
+        return prompt_kernel(q, k, v, out, cu, lens, table, page, num_seqs, max_q, *rest, **options)
 
     monkeypatch.setattr(ops, "attention_prefill_tcgen05", spy)
     got = _logits(path, "bfloat16", steps)

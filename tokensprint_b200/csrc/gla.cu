@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     stage(t0);
     __syncthreads();
     if (t0 + tb < t_end) fetch(t0 + tb);  // in flight while this round's updates run
-#pragma unroll 4
+#pragma unroll(KP > 16 ? 1 : 4)  // several tokens' loads and shuffles in flight where the registers allow
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = sv[tt * cols_per_cta + cj];
       // a thread's KP channels are a multiple of four and start on a 16-byte boundary: 16-byte loads
