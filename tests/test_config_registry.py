@@ -109,7 +109,9 @@ def test_listing_script():
     import model_registry
 
     out = model_registry.listing()
-    assert out.startswith("Registered models:\n\nfegetar:\n") and "\n\nqwen:\n" in out  # families in alphabetical order
+    assert out.startswith("Registered models:\n\ndazilix:\n") and "\n\nfegetar:\n" in out and "\n\nqwen:\n" in out
+    assert out.index("dazilix:") < out.index("fegetar:") < out.index("qwen:")  # families in alphabetical order
+    assert "  - dazilix-w2048 (dazilix/dazilix-w2048)" in out
     assert "  - fegetar-w2048 (fegetar/fegetar-w2048)" in out
     assert "  - qwen3-0.6b (qwen/qwen3-0.6b)" in out
     for name in ("qwen3-1.7b", "qwen3-4b", "qwen3-8b", "qwen3-14b", "qwen3-32b"):

@@ -96,7 +96,7 @@ def test_mixed_with_pages_and_slots_used_again(models, tag, page, dtype):
     folder, cfg, requests, oracle = models[tag, dtype]
     many = dict(requests)
     many.update({k + "x": v for k, v in requests.items()})
-    max_tokens = {"a": 320, "b": 384, "c": 448}[tag]
+    max_tokens = {"a": 320, "b": 384, "c": 456}[tag]
     steps = trace_mixed(many, max_tokens, seed=9, max_live=3)
     replayer = _replayer(folder, dtype, max_tokens, page, max_live=3)
     got = replay_in_process(replayer, steps)
