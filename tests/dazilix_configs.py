@@ -70,8 +70,19 @@ DAZ_C = {
     ],
 }
 
-DAZ = {"a": DAZ_A, "b": DAZ_B, "c": DAZ_C}
-DECAY_RANK = {"a": 6, "b": 5, "c": 0}  # the inner width of the decay's matrices: in no configuration key, only in the tensors
+# heads of 128 (the widths at which prompt attention runs on the tcgen05 kernel), one key/value head for both query heads,
+# blocks of 48 positions; a recurrent layer as wide; the first layer alone runs twice
+DAZ_D = {
+    "architecture": "Dazilix", "vocab": 180, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+    "loop": {"start": 0, "stop": 1, "times": 2},
+    "layers": [
+        _layer(_att(2, 1, 128, 48, 64), _moe(6, 2, 64)),
+        _layer(_gla(2, 128, 64, 12.0), None),
+    ],
+}
+
+DAZ = {"a": DAZ_A, "b": DAZ_B, "c": DAZ_C, "d": DAZ_D}
+DECAY_RANK = {"a": 6, "b": 5, "c": 0, "d": 8}  # the inner width of the decay's matrices: in no configuration key, only in the tensors
 
 
 def tensor_shapes(cfg: dict, decay_rank: int) -> dict[str, tuple[int, ...]]:

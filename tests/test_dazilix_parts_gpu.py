@@ -152,6 +152,64 @@ def test_block_edges_and_far_keys_show(kernel, dtype):
             assert _rel(got, want) < TOL[dtype], (query, key)
 
 
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("d, nq, nkv", [(64, 4, 2), (128, 8, 1), (32, 2, 2)])
+def test_decode_with_the_keys_split_over_ctas_keeps_bound_and_sink(d, nq, nkv, cluster):
+    """Single decoded tokens of three sequences of unequal length, the keys of each cut into 1 to 8
+    ranges that separate CTAs take and a merge puts together (inside a thread-block cluster, or by a
+    second kernel): the sink must be counted once, whichever range is empty, and the block bound hold."""
+    from tokensprint_b200 import ops
+
+    page, dtype, scale = 16, torch.bfloat16, 0.2
+    lens = [700, 37, 300]
+    B = len(lens)
+    ops._attention_mma_fns(d)  # loads the library of this head size, so that its merge mode can be set below
+    for chunk in (0, 256, 48):
+        for sink in (0.0, None, 1.5):
+            qs, want, pools_k, pools_v, tables = [], [], [], [], []
+            base = 0
+            for b, n in enumerate(lens):
+                q, k, v = (_randn(n, h, d, seed=100 * b + s).to(dtype).double() for h, s in ((nq, 1), (nkv, 2), (nkv, 3)))
+                ref = _plain_attend(q, k, v, range(n), nq, nkv, scale, chunk, False) if sink is None else None
+                if sink is not None:  # a sink of any score: one more key of that score whose value is zero
+                    p = torch.arange(n)
+                    visible = p[None, :] <= p[:, None]
+                    if chunk:
+                        visible &= (p[None, :] // chunk) == (p[:, None] // chunk)
+                    ref = torch.empty(n, nq, d, dtype=torch.float64)
+                    for h in range(nq):
+                        sc = (q[:, h] @ k[:, h // (nq // nkv)].T) * scale
+                        sc = torch.cat([sc.masked_fill(~visible, -math.inf), torch.full((n, 1), sink, dtype=torch.float64)], dim=1)
+                        ref[:, h] = torch.softmax(sc, dim=1)[:, :n] @ v[:, h // (nq // nkv)]
+                qs.append(q[n - 1])
+                want.append(ref[n - 1])
+                kp, table = _paged(k, page, dtype, 20 + b)
+                vp, _ = _paged(v, page, dtype, 20 + b)
+                pools_k.append(kp)
+                pools_v.append(vp)
+                tables.append(table + base)
+                base += kp.shape[0]
+            kpool, vpool = torch.cat(pools_k), torch.cat(pools_v)
+            width = max(len(t) for t in tables)
+            table = torch.full((B, width), -1, dtype=torch.int32)
+            for b, t in enumerate(tables):
+                table[b, : len(t)] = t
+            qd = torch.stack(qs).reshape(B, nq * d).to(dtype).to(DEV)
+            cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+            ctx = torch.tensor(lens, dtype=torch.int32, device=DEV)
+            seq = torch.arange(B, dtype=torch.int32, device=DEV)
+            for splits in (1, 2, 5, 8):
+                out = torch.empty((B, nq * d), device=DEV, dtype=dtype)
+                scratch = torch.empty(ops.attention_scratch_floats(B * nq, splits, d), device=DEV, dtype=torch.float32) if splits > 1 else None
+                ops._attention_flat[d].ts_attention_mma_set_cluster_merge(1 if cluster else 0) if d in ops._attention_flat else None
+                ops.attention_paged_mma(qd, kpool, vpool, out, cu, ctx, table.to(DEV), seq, page, B, 1, nq, nkv, d, scale, 0, splits, scratch, 0,
+                                        chunk=chunk, sink=sink)
+                if d in ops._attention_flat:
+                    ops._attention_flat[d].ts_attention_mma_set_cluster_merge(1 if ops.ATTENTION_CLUSTER_MERGE else 0)
+                torch.cuda.synchronize()
+                assert _rel(out.view(B, nq, d), torch.stack(want)) < TOL[dtype], (chunk, sink, splits)
+
+
 @pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_sink_takes_its_share(kernel, dtype):

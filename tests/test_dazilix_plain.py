@@ -109,7 +109,7 @@ def test_logits_of_a_prefix_do_not_depend_on_what_follows(tag):
 # the engine's configuration, registry and run order (no GPU needed)
 
 
-@pytest.mark.parametrize("tag", ["a", "b", "c"])
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d"])
 def test_config_and_tensor_names(tag):
     from tokensprint_b200.config.registry import architecture_for
 

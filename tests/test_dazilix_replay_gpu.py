@@ -22,9 +22,9 @@ pytestmark = pytest.mark.gpu
 TOLERANCE = {"float32": 1e-4, "bfloat16": 8e-2}
 SHARP = {"float32": 3.0, "bfloat16": 1.0}
 ROUTED_SHARE = {"float32": 1.0, "bfloat16": 0.02}
-LENGTHS = {"a": [1, 5, 17, 64, 100, 131], "b": [2, 9, 33, 90, 150], "c": [3, 26, 70, 129, 190]}
-SEEDS = {"a": 51, "b": 52, "c": 53}
-CASES = [("a", 16), ("b", 16), ("c", 16), ("a", 8), ("c", 32), ("a", 256)]
+LENGTHS = {"a": [1, 5, 17, 64, 100, 131], "b": [2, 9, 33, 90, 150], "c": [3, 26, 70, 129, 190], "d": [4, 40, 97, 150, 200]}
+SEEDS = {"a": 51, "b": 52, "c": 53, "d": 54}
+CASES = [("a", 16), ("b", 16), ("c", 16), ("d", 16), ("a", 8), ("c", 32), ("a", 256), ("d", 64)]
 
 
 class Oracle:
@@ -96,7 +96,7 @@ def test_mixed_with_pages_and_slots_used_again(models, tag, page, dtype):
     folder, cfg, requests, oracle = models[tag, dtype]
     many = dict(requests)
     many.update({k + "x": v for k, v in requests.items()})
-    max_tokens = {"a": 320, "b": 384, "c": 456}[tag]
+    max_tokens = {"a": 320, "b": 384, "c": 456, "d": 512}[tag]
     steps = trace_mixed(many, max_tokens, seed=9, max_live=3)
     replayer = _replayer(folder, dtype, max_tokens, page, max_live=3)
     got = replay_in_process(replayer, steps)
@@ -110,7 +110,7 @@ def test_mixed_with_pages_and_slots_used_again(models, tag, page, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["a", "b", "c"])
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d"])
 def test_batches_of_unequal_requests_against_each_alone(models, tag, dtype):
     """The same positions alone and in a batch of unequal requests: equal beyond rounding."""
     folder, cfg, requests, oracle = models[tag, dtype]
@@ -144,7 +144,7 @@ def test_chunk_groups_give_pages_back_while_a_request_grows(models, tag, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("tag", ["a", "b"])
 def test_long_decoding_with_graphs_and_without(models, tag, dtype):
-    """One prompt token, then 200 tokens one by one, beside a second request that decodes too."""
+    """One prompt token, then more than a hundred tokens one by one, beside a second request that decodes too."""
     folder, cfg, requests, oracle = models[tag, dtype]
     reqs = {"p": requests["r4"][:1] + requests["r3"] + requests["r2"], "q": requests["r4"]}
     first = min(90, len(reqs["q"]) - 1)

@@ -55,7 +55,7 @@ class BlockAttentionConfig:
     scale: float
     rot_base: float
     rot_dims: int
-    mask_size: int
+    mask_size: int  # 0: no `mask` in the file, every earlier key is seen
 
     @classmethod
     def from_dict(cls, d: dict[str, Any], where: str) -> "BlockAttentionConfig":
@@ -63,20 +63,23 @@ class BlockAttentionConfig:
         c = cls(heads=require(d, "heads", int), kv_heads=require(d, "kv_heads", int), dim=require(d, "dim", int),
                 vdim=require(d, "vdim", int), scale=require(d, "scale", float),
                 rot_base=require(rot, "base", float) if rot else 1.0, rot_dims=require(rot, "dims", int) if rot else 0,
-                mask_size=require(_section(d, "mask", where), "size", int))
+                mask_size=require(_section(d, "mask", where), "size", int) if d.get("mask") is not None else 0)
         if min(c.heads, c.kv_heads, c.dim) < 1 or c.heads % c.kv_heads:
             raise ConfigError(f"config.json: {where}heads must be a positive multiple of kv_heads, dim positive")
         if c.vdim != c.dim:
             raise ConfigError(f"config.json: {where}the values are the key projection, so vdim must equal dim")
         if c.rot_dims % 2 or not 0 <= c.rot_dims <= c.dim or (c.rot_dims and c.rot_base <= 0):
             raise ConfigError(f"config.json: {where}rot.dims must be even and at most dim, rot.base positive")
-        if c.mask_size < 1:
+        if c.mask_size < 0 or (d.get("mask") is not None and c.mask_size < 1):
             raise ConfigError(f"config.json: {where}mask.size must be positive")
         return c
 
     def to_dict(self) -> dict[str, Any]:
-        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-                "rot": {"base": self.rot_base, "dims": self.rot_dims}, "mask": {"size": self.mask_size}}
+        d = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
+             "rot": {"base": self.rot_base, "dims": self.rot_dims}}
+        if self.mask_size:
+            d["mask"] = {"size": self.mask_size}
+        return d
 
 
 @dataclass(frozen=True)
@@ -184,7 +187,7 @@ class DazilixConfig:
                  "max_position_embeddings", "eos_token_id"}
         return cls(
             vocab=require(d, "vocab", int), width=require(d, "width", int), norm_eps=require(_section(d, "norm", ""), "eps", float),
-            embedding_scale=require(_section(d, "embedding", ""), "scale", float), layers=tuple(layers),
+            embedding_scale=require(d["embedding"], "scale", float) if isinstance(d.get("embedding"), dict) else 1.0, layers=tuple(layers),
             loop_start=require(loop, "start", int) if loop else 0, loop_stop=require(loop, "stop", int) if loop else 0,
             loop_times=require(loop, "times", int) if loop else 0,
             max_position_embeddings=int(d.get("max_position_embeddings") or DEFAULT_MAX_POSITIONS),
