@@ -345,6 +345,42 @@ def test_gla_scan_unequal_sequences_and_portions(dtype, H, d, e):
     assert torch.equal(state[3], before[3]) and not torch.equal(state[1], before[1])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, d, e", [(2, 20, 28), (1, 64, 128), (2, 7, 10)])
+def test_gla_scan_long_portions_in_segments(dtype, H, d, e):
+    """Portions long enough to be cut into segments that run side by side, beside a short one and a
+    single token, each starting from a state that is not zero: against the plain recurrence, and
+    against the same tokens run in one piece."""
+    from tokensprint_b200 import ops
+
+    lens, tau, q_scale = [1300, 5, 1, 700], 9.0, d ** -0.5
+    T = sum(lens)
+    q, k, v, z, bias = _gla_inputs(T, H, d, e, dtype, 40)
+    wide = torch.cat([q, k, v], dim=1).to(DEV)
+    qd, kd, vd = wide[:, : H * d], wide[:, H * d : 2 * H * d], wide[:, 2 * H * d :]
+    zd, bd = z.to(DEV), (bias + 2.0).to(DEV)  # decays near one: what a segment starts from matters to its end
+    start = (0.3 * _randn(6, H, d, e, seed=41)).float()
+    slots = torch.tensor([5, 0, 3, 2], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 1300, 1305, 1306, 2006], dtype=torch.int32, device=DEV)
+    results = []
+    for max_seqlen in (max(lens), None):
+        assert (ops.gla_segments(4, max_seqlen)[0] > 1) == (max_seqlen is not None)
+        state = start.clone().to(DEV)
+        out = torch.empty((T, H * e), device=DEV, dtype=torch.float32)
+        ops.gla_scan(qd, kd, vd, zd, bd, tau, q_scale, state, slots, cu, out, 4, H, d, e, max_seqlen=max_seqlen)
+        torch.cuda.synchronize()
+        results.append((out, state))
+    begin = 0
+    for b, n in enumerate(lens):
+        sl = slice(begin, begin + n)
+        want, final = _plain_gla(q[sl], k[sl], v[sl], z[sl], bias + 2.0, tau, q_scale, H, d, e, state=start[int(slots[b])].double())
+        for out, state in results:
+            assert _rel(out[sl], want) < 5e-5, f"sequence {b}"
+            assert _rel(state[int(slots[b])], final) < 5e-5, f"state of sequence {b}"
+        begin += n
+    assert torch.equal(results[0][1][1].cpu(), start[1]) and torch.equal(results[0][1][4].cpu(), start[4]), "a slot of no sequence was touched"
+
+
 def test_gla_state_remembers_a_far_token():
     """Decays of one on one key channel: a value written 600 tokens ago is read back exactly by a
     query on that channel; a channel whose decay is small has forgotten it."""

@@ -49,11 +49,19 @@ __device__ __forceinline__ __nv_bfloat16 gla_load(const __nv_bfloat16* p) {
 // The rounds are pipelined: while the threads run the updates of one round from shared memory, the
 // loads of the next round's q, k, z and v are in flight into registers (issued before the updates,
 // used after them), so the recurrence never waits for device memory.
-template <typename TA, int KP>
+//
+// Long portions are cut into `segs` segments of `seg_len` tokens that run side by side (the recurrence
+// is linear in the state): MODE 1 runs every segment but a sequence's last from a zero state (the
+// first from the request's state) and leaves the state it ends with and the product of its decays;
+// MODE 2 starts every segment from what the segments before it left, folded in order
+// (S <- product * S + state), writes the read-outs, and the last segment writes the request's slot.
+// MODE 0 is the whole portion in one piece (decode steps, short portions: the same sums whatever the cut).
+template <typename TA, int KP, int MODE>
 __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const float* __restrict__ decay,
     float q_scale, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
-    float* __restrict__ o, int H, int d, int e, int R, int cols_per_cta, int tb) {
+    float* __restrict__ o, int H, int d, int e, int R, int cols_per_cta, int tb, int segs, int seg_len, float* __restrict__ seg_state,
+    float* __restrict__ seg_decay, float* __restrict__ seg_start) {
   ts_pdl_prologue();
   extern __shared__ __align__(16) float sm[];
   // staged per token: q, k, decay [dp] each, v [cols]
@@ -62,17 +70,55 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   float* sk = sq + tb * dp;
   float* sa = sk + tb * dp;
   float* sv = sa + tb * dp;  // [tb][cols_per_cta]
-  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_cta;
-  const int t_begin = cu_seqlens[b], t_end = cu_seqlens[b + 1];
+  const int b = MODE == 0 ? blockIdx.x : blockIdx.x / segs, seg = MODE == 0 ? 0 : blockIdx.x - b * segs;
+  const int h = blockIdx.y, col0 = blockIdx.z * cols_per_cta;
+  const int t_begin = cu_seqlens[b] + seg * seg_len, t_end = MODE == 0 ? cu_seqlens[b + 1] : min(cu_seqlens[b + 1], t_begin + seg_len);
   if (t_end <= t_begin) return;
+  const bool last = t_end == cu_seqlens[b + 1];
+  if (MODE == 1 && last) return;  // nobody starts from what a sequence's last segment leaves
   const int r = threadIdx.x % R, cj = threadIdx.x / R;  // lanes of one column sit side by side
   const int col = col0 + cj;
   const bool has_col = col < e;
   const int c0 = r * KP;
   float* S = state + (((size_t)state_slots[b] * H + h) * d) * e;
+  const size_t state_elems = (size_t)d * e;
+  float* seg_L = MODE == 0 ? nullptr : seg_state + (((size_t)b * segs + seg) * H + h) * state_elems;   // this segment's end state
+  float* seg_P = MODE == 0 ? nullptr : seg_decay + (((size_t)b * segs + seg) * H + h) * d;             // this segment's decay product
+  float* seg_S0 = MODE == 0 ? nullptr : seg_start + ((size_t)b * H + h) * state_elems;                 // the request's state as the step found it
   float s_reg[KP];
+  float p_reg[MODE == 1 ? KP : 1];
+  if (MODE == 0 || (seg == 0 && (MODE == 1 || last))) {
+    // the request's state (MODE 2: only a sequence of one segment reads the slot, which it alone writes in this launch)
 #pragma unroll
-  for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? S[(size_t)(c0 + i) * e + col] : 0.f;
+    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? S[(size_t)(c0 + i) * e + col] : 0.f;
+    if (MODE == 1 && has_col) {
+#pragma unroll
+      for (int i = 0; i < KP; ++i)
+        if (c0 + i < d) seg_S0[(size_t)(c0 + i) * e + col] = s_reg[i];
+    }
+  } else if (MODE == 1) {
+#pragma unroll
+    for (int i = 0; i < KP; ++i) s_reg[i] = 0.f;
+  } else if (seg == 0) {
+#pragma unroll
+    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? seg_S0[(size_t)(c0 + i) * e + col] : 0.f;
+  } else {
+    // what the segments before left, folded in order (the first one's end state already holds the request's state)
+    const float* L = seg_state + (((size_t)b * segs) * H + h) * state_elems;
+#pragma unroll
+    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? L[(size_t)(c0 + i) * e + col] : 0.f;
+    for (int j = 1; j < seg; ++j) {
+      L = seg_state + (((size_t)b * segs + j) * H + h) * state_elems;
+      const float* P = seg_decay + (((size_t)b * segs + j) * H + h) * d;
+#pragma unroll
+      for (int i = 0; i < KP; ++i)
+        if (has_col && c0 + i < d) s_reg[i] = fmaf(P[c0 + i], s_reg[i], L[(size_t)(c0 + i) * e + col]);
+    }
+  }
+  if (MODE == 1) {
+#pragma unroll
+    for (int i = 0; i < KP; ++i) p_reg[i] = 1.f;
+  }
 
   const size_t qk_off = (size_t)h * d, v_off = (size_t)h * e + col0;
   // what this thread fetches for a round: entries threadIdx.x + j * GLA_THREADS of the round's [tokens][dp] and [tokens][cols]
@@ -148,52 +194,91 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
       float acc[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: the read-out is a sum of KP terms, its order is fixed by KP alone
 #pragma unroll
       for (int i = 0; i < KP / 4; ++i) {
-        const float4 a4 = pa[i], k4 = pk[i], q4 = pq[i];
+        const float4 a4 = pa[i], k4 = pk[i];
         s_reg[4 * i + 0] = fmaf(a4.x, s_reg[4 * i + 0], k4.x * vv);
         s_reg[4 * i + 1] = fmaf(a4.y, s_reg[4 * i + 1], k4.y * vv);
         s_reg[4 * i + 2] = fmaf(a4.z, s_reg[4 * i + 2], k4.z * vv);
         s_reg[4 * i + 3] = fmaf(a4.w, s_reg[4 * i + 3], k4.w * vv);
-        acc[0] = fmaf(s_reg[4 * i + 0], q4.x, acc[0]);
-        acc[1] = fmaf(s_reg[4 * i + 1], q4.y, acc[1]);
-        acc[2] = fmaf(s_reg[4 * i + 2], q4.z, acc[2]);
-        acc[3] = fmaf(s_reg[4 * i + 3], q4.w, acc[3]);
+        if (MODE == 1) {  // no read-outs yet: the product of the segment's decays instead
+          p_reg[(MODE == 1 ? 4 * i : 0) + 0] *= a4.x;
+          p_reg[(MODE == 1 ? 4 * i + 1 : 0)] *= a4.y;
+          p_reg[(MODE == 1 ? 4 * i + 2 : 0)] *= a4.z;
+          p_reg[(MODE == 1 ? 4 * i + 3 : 0)] *= a4.w;
+        } else {
+          const float4 q4 = pq[i];
+          acc[0] = fmaf(s_reg[4 * i + 0], q4.x, acc[0]);
+          acc[1] = fmaf(s_reg[4 * i + 1], q4.y, acc[1]);
+          acc[2] = fmaf(s_reg[4 * i + 2], q4.z, acc[2]);
+          acc[3] = fmaf(s_reg[4 * i + 3], q4.w, acc[3]);
+        }
       }
-      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      for (int w = 1; w < R; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
-      if (r == 0 && has_col) o[((size_t)(t0 + tt) * H + h) * e + col] = sum;
+      if (MODE != 1) {
+        float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        for (int w = 1; w < R; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+        if (r == 0 && has_col) o[((size_t)(t0 + tt) * H + h) * e + col] = sum;
+      }
     }
   }
-  if (has_col) {
+  if (MODE == 1) {
+    if (has_col) {
+#pragma unroll
+      for (int i = 0; i < KP; ++i)
+        if (c0 + i < d) seg_L[(size_t)(c0 + i) * e + col] = s_reg[i];
+    }
+    if (blockIdx.z == 0 && cj == 0) {  // the decays do not depend on the column: one thread per group of channels writes them
+#pragma unroll
+      for (int i = 0; i < KP; ++i)
+        if (c0 + i < d) seg_P[c0 + i] = p_reg[MODE == 1 ? i : 0];
+    }
+  } else if (has_col && (MODE == 0 || last)) {
 #pragma unroll
     for (int i = 0; i < KP; ++i)
       if (c0 + i < d) S[(size_t)(c0 + i) * e + col] = s_reg[i];
   }
 }
 
-template <typename TA, int KP>
+template <typename TA, int KP, int MODE>
 static int launch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
-                           const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int R, cudaStream_t s) {
+                           const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int R, int segs, int seg_len,
+                           float* scratch, cudaStream_t s) {
   const int cols = GLA_THREADS / R, dp = R * KP;
   // tokens per round: what the threads' fetch registers hold, at most GLA_TB
   const int tb = min(GLA_TB, min(GLA_THREADS * GLA_PF / dp, GLA_THREADS * GLA_PFV / cols));
   if (tb < 1) return TS_ERR_UNSUPPORTED_SIZE;
   const size_t smem = (size_t)tb * (3 * dp + cols) * sizeof(float);  // at most 16 * (3 * 64 + 128) or 1 * (3 * 1024 + 4) floats: below 48 KB
-  const dim3 grid(B, H, (e + cols - 1) / cols);
+  const dim3 grid(B * segs, H, (e + cols - 1) / cols);
   if (grid.y > 65535 || grid.z > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(gla_scan_kernel<TA, KP>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, decay, q_scale,
-                   state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb);
+  // scratch of the segmented scan: end states [B, segs, H, d, e], decay products [B, segs, H, d], start states [B, H, d, e]
+  float* seg_state = scratch;
+  float* seg_decay = scratch ? seg_state + (size_t)B * segs * H * d * e : nullptr;
+  float* seg_start = scratch ? seg_decay + (size_t)B * segs * H * d : nullptr;
+  return ts_launch(gla_scan_kernel<TA, KP, MODE>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, decay,
+                   q_scale, state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb, segs, seg_len, seg_state, seg_decay, seg_start);
+}
+
+template <typename TA, int KP>
+static int launch_gla_scan_modes(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
+                                 const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int R, int segs,
+                                 int seg_len, float* scratch, cudaStream_t s) {
+  if (segs <= 1)
+    return launch_gla_scan<TA, KP, 0>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, 1, 0, nullptr, s);
+  const int st = launch_gla_scan<TA, KP, 1>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len,
+                                            scratch, s);
+  if (st != 0) return st;
+  return launch_gla_scan<TA, KP, 2>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len, scratch, s);
 }
 
 template <typename TA>
 static int dispatch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
-                             const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, cudaStream_t s) {
+                             const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int segs, int seg_len,
+                             float* scratch, cudaStream_t s) {
   // R lanes per column, a power of two, so that a thread holds at most GLA_MAX_KP channels
   int R = 1;
   while (R < 32 && (d + R - 1) / R > GLA_MAX_KP) R <<= 1;
   // more lanes per column (fewer channels per thread, more CTAs) while the grid would leave SMs idle
   // or a thread's chain of updates per token would be long; a function of the sizes and the batch alone
   while (R < 32 && (d + R - 1) / R > 4 &&
-         ((d + R - 1) / R > 16 || (long long)B * H * ((e + GLA_THREADS / R - 1) / (GLA_THREADS / R)) < 2 * 148))
+         ((d + R - 1) / R > 16 || (long long)B * max(segs, 1) * H * ((e + GLA_THREADS / R - 1) / (GLA_THREADS / R)) < 2 * 148))
     R <<= 1;
   if (const char* forced = getenv("TS_GLA_LANES")) {  // for measurements: a fixed number of lanes per column
     const int want = atoi(forced);
@@ -203,7 +288,8 @@ static int dispatch_gla_scan(const void* q, const void* k, const void* v, long l
   if (kp > GLA_MAX_KP) return TS_ERR_UNSUPPORTED_SIZE;  // d > 1024
   static_assert(GLA_MAX_KP % 4 == 0, "a thread's channels come in fours");
 #define GLA_CASE(KP) \
-  if (kp <= KP) return launch_gla_scan<TA, KP>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, s)
+  if (kp <= KP) \
+    return launch_gla_scan_modes<TA, KP>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len, scratch, s)
   GLA_CASE(4);
   GLA_CASE(8);
   GLA_CASE(12);
@@ -243,17 +329,28 @@ TS_EXPORT int ts_gla_decay(const void* z, long long ld_z, int act_dtype, const f
   return TS_ERR_BAD_ARGUMENT;
 }
 
+// Floats of scratch that a scan of B sequences in `segs` segments each needs.
+TS_EXPORT long long ts_gla_scan_scratch_floats(int B, int segs, int H, int d, int e) {
+  if (segs <= 1) return 0;
+  return (long long)B * segs * H * d * e + (long long)B * segs * H * d + (long long)B * H * d * e;
+}
+
 // q, k [T, H*d] and v [T, H*e] are views with the common row stride ld_qkv (columns of one product's
 // result); decay [T, H*d] float32 (gla_decay); state [slots, H, d, e] float32; o [T, H*e] float32.
+// segs > 1: every sequence's tokens of the step are cut into segments of seg_len tokens (segs * seg_len
+// covers the longest) that run side by side, through `scratch` (ts_gla_scan_scratch_floats); two launches.
 TS_EXPORT int ts_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, int act_dtype, const float* decay, float q_scale,
-                          float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, void* stream) {
+                          float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int segs,
+                          int seg_len, float* scratch, void* stream) {
   if (B <= 0) return 0;
-  if (H <= 0 || d <= 0 || e <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (H <= 0 || d <= 0 || e <= 0 || segs < 1 || (segs > 1 && (seg_len < 1 || scratch == nullptr))) return TS_ERR_BAD_ARGUMENT;
+  if ((long long)B * segs > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    return dispatch_gla_scan<float>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, s);
+    return dispatch_gla_scan<float>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len, scratch, s);
   if (act_dtype == TS_DTYPE_BF16)
-    return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, s);
+    return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len,
+                                            scratch, s);
   return TS_ERR_BAD_ARGUMENT;
 }
 

@@ -64,7 +64,7 @@ _SIGNATURES = {
                                     _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_gla_decay": [_c_void_p, _c_ll, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_void_p],
     "ts_gla_scan": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-                    _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "ts_gla_norm_gate": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "ts_branch_norm_add": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float,
                            _c_void_p],
@@ -649,11 +649,26 @@ def qk_joint_norm_rope_store(qk: torch.Tensor, q_out: torch.Tensor, k_dst: torch
 
 
 GLA_MAX_KEY_DIM = 1024
+GLA_SEGMENT_TOKENS = 256  # a portion of at least twice as many tokens is cut into segments that run side by side
+GLA_MAX_SEGMENTS = 64     # segments of all sequences of a step together (their end states live in scratch)
+
+
+def gla_segments(num_seqs: int, max_seqlen: Optional[int]) -> tuple[int, int]:
+    """(segments per sequence, tokens per segment) of a step whose longest portion has `max_seqlen`
+    tokens; (1, 0): every portion in one piece.  A function of the batch's size and its longest
+    portion alone."""
+    if max_seqlen is None or max_seqlen < 2 * GLA_SEGMENT_TOKENS:
+        return 1, 0
+    seg_len = GLA_SEGMENT_TOKENS
+    while num_seqs * -(-max_seqlen // seg_len) > GLA_MAX_SEGMENTS and seg_len < max_seqlen:
+        seg_len *= 2
+    segs = -(-max_seqlen // seg_len)
+    return (segs, seg_len) if segs > 1 else (1, 0)
 
 
 def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor], tau: float, q_scale: float,
              state: torch.Tensor, state_slots: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor, num_seqs: int, num_heads: int,
-             key_dim: int, value_dim: int) -> None:
+             key_dim: int, value_dim: int, max_seqlen: Optional[int] = None) -> None:
     """The recurrence of gated linear attention over the step's tokens, sequence by sequence:
     decay = sigmoid(z + bias)^(1/tau) per key channel, S <- diag(decay) S + k v^T, out = S^T (q * q_scale).
 
@@ -661,7 +676,11 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     z [T, H*d] with its own; bias [H*d] float32 or None; state [slots, H, d, e] float32, read at a
     sequence's slot before its first token of the step and written after its last; state_slots [B],
     cu_seqlens [B+1] int32; out [T, H*e] float32.  Everything but the loads is float32.  Two launches:
-    the decays of all tokens and channels once (float32 scratch [T, H*d]), then the recurrence."""
+    the decays of all tokens and channels once (float32 scratch [T, H*d]), then the recurrence.
+    `max_seqlen`: the most tokens a sequence brings; given, long portions are cut into segments that
+    run side by side (gla_segments; two launches of the recurrence: every segment's end state and
+    decay product from a zero state, then the read-outs from the folded start states).  The sums of a
+    token then depend on where its portion began, in the order of float32 rounding."""
     flush_gemm_chain()
     H, d, e = int(num_heads), int(key_dim), int(value_dim)
     if d > GLA_MAX_KEY_DIM:
@@ -687,9 +706,17 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     decay = torch.empty((T, H * d), device=q.device, dtype=torch.float32)
     code, stream = _act_code("q", q), _stream()
     _check("gla_scan", _fn("ts_gla_decay")(z.data_ptr(), z.stride(0), code, _ptr(bias), float(tau), decay.data_ptr(), T, H * d, stream))
+    segs, seg_len = gla_segments(int(num_seqs), max_seqlen)
+    scratch = None
+    if segs > 1:
+        need = int(num_seqs) * segs * H * d * e + int(num_seqs) * segs * H * d + int(num_seqs) * H * d * e
+        scratch = torch.empty(need, device=q.device, dtype=torch.float32)
     _check("gla_scan", _fn("ts_gla_scan")(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), code, decay.data_ptr(), float(q_scale), state.data_ptr(),
-        state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, d, e, stream))
+        state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, d, e, segs, seg_len, _ptr(scratch), stream))
+    if segs > 1:
+        global launch_count
+        launch_count += 1  # the recurrence ran as two kernels
 
 
 def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_heads: int, value_dim: int, eps: float) -> None:

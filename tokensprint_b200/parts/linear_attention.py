@@ -97,7 +97,7 @@ class GatedLinearAttention(Mixer):
         z = linear(low, self.decay_out, next_weight=self.o_weight)
         o = torch.empty((T, he), device=x.device, dtype=torch.float32)
         ops.gla_scan(q, k, v, z, self.decay_bias, self.tau, self.q_scale, cache.state, step.state_slots, step.cu_seqlens_q, o,
-                     step.num_seqs, H, d, e)
+                     step.num_seqs, H, d, e, max_seqlen=step.max_seqlen_q)
         y = torch.empty((T, he), device=x.device, dtype=x.dtype)
         ops.gla_norm_gate(o, gate, self.norm_weight, y, H, e, self.norm_eps)
         return linear(y, self.o_weight, next_weight=step.weight_after)
