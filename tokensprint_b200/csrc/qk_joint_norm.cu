@@ -182,7 +182,9 @@ TS_EXPORT int ts_qk_joint_norm_rope_store(const void* qk, int act_dtype, long lo
   if (smem <= 40 * 1024) {
     const size_t elem = act_dtype == TS_DTYPE_F32 ? 4 : 2;
     const int wide = (n % 4 == 0 && (nq * d) % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qk % (4 * elem)) == 0) ? 1 : 0;
-    const int th = wide ? min(512, max(64, (n / 4 + 31) / 32 * 32)) : threads;
+    // Few tokens: a row's pieces spread over many threads (shortest latency).  Many: smaller CTAs (16 entries a thread), so that
+    // an SM holds more tokens at once and one token's load, reduction and store phases overlap with the others'.
+    const int th = T >= 512 ? min(512, max(128, (n / 16 + 31) / 32 * 32)) : (wide ? min(512, max(64, (n / 4 + 31) / 32 * 32)) : threads);
     if (act_dtype == TS_DTYPE_F32)
       return ts_launch(qk_joint_norm_rope_store_staged_kernel<float>, dim3(T), dim3(th), smem, s, (const float*)qk, ld, (float*)q_out,
                        (float*)k_dst, (float*)v_dst, slot_mapping, q_w, k_w, eps, cos_sin, rot, nq, nkv, d, wide);
