@@ -81,6 +81,19 @@ DAZ_D = {
     ],
 }
 
+# for one long request: blocks of 512 and 1,024 positions (a decoded token's keys are then split over several CTAs, a far key
+# is hundreds of positions back), heads of 128 and of 64, two recurrent layers of different shapes, the middle stretch twice
+DAZ_LONG = {
+    "architecture": "Dazilix", "vocab": 500, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
+    "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [
+        _layer(_att(8, 2, 128, 512, 64), _moe(8, 2, 96)),
+        _layer(_gla(4, 32, 64, 16.0), _moe(8, 2, 96)),
+        _layer(_att(4, 4, 64, 1024, 32, scale=0.2), None),
+        _layer(_gla(2, 128, 128, 8.0), _moe(3, 1, 64)),
+    ],
+}
+
 DAZ = {"a": DAZ_A, "b": DAZ_B, "c": DAZ_C, "d": DAZ_D}
 DECAY_RANK = {"a": 6, "b": 5, "c": 0, "d": 8}  # the inner width of the decay's matrices: in no configuration key, only in the tensors
 

@@ -166,6 +166,25 @@ def test_long_decoding_with_graphs_and_without(models, tag, dtype):
         assert float(abs(row - results[1][key]).max()) <= TOLERANCE[dtype] * float(abs(row).max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_request_whole_decoded_and_in_portions(tmp_path, dtype):
+    """1,200 tokens through blocks of 512 and 1,024 positions: prompt attention over hundreds of keys (heads
+    of 128: the tcgen05 kernel), decoded tokens whose keys are split over several CTAs, the recurrence in
+    segments side by side (portions of 520 and 700 tokens) and in one piece, with graphs and without."""
+    from tests.dazilix_configs import DAZ_LONG as cfg
+
+    ids = random_ids(cfg, 1200, 7)
+    reqs = {"r": ids}
+    weights = dazilix_weights(cfg, 77, decay_rank=12, sharp=SHARP[dtype], routed_share=ROUTED_SHARE[dtype])
+    folder = write_dazilix_folder(tmp_path / "long", cfg, weights)
+    oracle = Oracle(cfg, weights)
+    runs = [("whole", trace_whole(reqs), False), ("decode tail", trace_decode_tail(reqs, 80), False), ("decode tail, graphs", trace_decode_tail(reqs, 80), True),
+            ("portions", trace_portions(reqs, (300, 2, 520, 64, 3, 700, 17)), False)]
+    for what, steps, graphs in runs:
+        replayer = _replayer(folder, dtype, 2048, graphs=graphs, max_model_len=2048)
+        _check(replay_in_process(replayer, steps), reqs, oracle, dtype, what)
+
+
 def _plain_greedy(weights, cfg, prompt, steps):
     ids = list(prompt)
     for _ in range(steps):
