@@ -72,21 +72,25 @@ __global__ void qk_joint_norm_rope_store_kernel(const TA* __restrict__ qk, long 
 }
 
 // The same through shared memory, for rows that fit it (every practical size): the row is read
-// once with the widest loads its alignment allows, partners of the rotation come from shared
-// memory, and q', k' and the values leave in pairs of elements.
+// once with the widest loads its alignment allows and staged with the norm weights already on it,
+// the values leave in that first pass, partners of the rotation come from shared memory, and
+// q' and k' leave in pairs of elements.
 template <typename TA>
 __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk, long long ld, TA* __restrict__ q_out, TA* __restrict__ k_dst,
                                                        TA* __restrict__ v_dst, const int* __restrict__ slot_mapping,
                                                        const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                                        const float* __restrict__ cos_sin, int rot, int nq, int nkv, int d, int wide) {
   ts_pdl_prologue();
-  extern __shared__ float xs[];  // the row [q | k] as float32
+  extern __shared__ float xs[];  // the row [q | k] times its norm weights, float32 (only the factor 1/rms is still missing)
   __shared__ float2 scratch2[33];
   const int t = blockIdx.x;
   const TA* row = qk + (size_t)t * ld;
   const int nQ = nq * d, nK = nkv * d, n = nQ + nK, half = rot >> 1;
+  const int slot = slot_mapping ? slot_mapping[t] : t;
   float sq = 0.f, sk = 0.f;
-  if (wide) {  // n, nQ and ld are multiples of 4 and the row starts on a 4-element boundary
+  // First pass: the sums of squares, the row times the weights into shared memory, and the values (the k row as it is)
+  // straight to their place: nothing of that waits for the norm.
+  if (wide) {  // n, nQ and ld are multiples of 4, the row, the weights and the value pool start on 4-element boundaries
     for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
       float v[4];
       if constexpr (sizeof(TA) == 2) {
@@ -99,14 +103,26 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
         v[0] = raw.x, v[1] = raw.y, v[2] = raw.z, v[3] = raw.w;
       }
       const float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-      if (i < nQ) sq += ss; else sk += ss;
-      *reinterpret_cast<float4*>(xs + i) = make_float4(v[0], v[1], v[2], v[3]);
+      const bool is_q = i < nQ;
+      if (is_q) sq += ss; else sk += ss;
+      const float4 w4 = *reinterpret_cast<const float4*>(is_q ? q_w + i : k_w + (i - nQ));
+      *reinterpret_cast<float4*>(xs + i) = make_float4(v[0] * w4.x, v[1] * w4.y, v[2] * w4.z, v[3] * w4.w);
+      if (!is_q && slot >= 0) {
+        TA* vd = v_dst + (size_t)slot * nK + (i - nQ);
+        if constexpr (sizeof(TA) == 2) {
+          *reinterpret_cast<uint2*>(vd) = *reinterpret_cast<const uint2*>(row + i);
+        } else {
+          *reinterpret_cast<float4*>(vd) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+      }
     }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const float v = ts_to_float(row[i]);
-      if (i < nQ) sq += v * v; else sk += v * v;
-      xs[i] = v;
+      const bool is_q = i < nQ;
+      if (is_q) sq += v * v; else sk += v * v;
+      xs[i] = v * (is_q ? q_w[i] : k_w[i - nQ]);
+      if (!is_q && slot >= 0) v_dst[(size_t)slot * nK + (i - nQ)] = row[i];
     }
   }
   {  // both sums of squares in one pass over the block (its barriers also make the staged row visible to all threads)
@@ -127,20 +143,16 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
   }
   const float rq = 1.f / sqrtf(sq / (float)nQ + eps), rk = 1.f / sqrtf(sk / (float)nK + eps);
   const float* cs = cos_sin + (size_t)t * half * 2;
-  const int slot = slot_mapping ? slot_mapping[t] : t;
   auto element = [&](int i, int j) -> float {  // entry i of [q' | k'], which is entry j of its head
-    const bool is_q = i < nQ;
-    const int e = is_q ? i : i - nQ;
-    const float* w = is_q ? q_w : k_w;
-    const float r = is_q ? rq : rk;
-    const float x = xs[i] * r * w[e];
-    if (j < half) return x * cs[2 * j] - xs[i + half] * r * w[e + half] * cs[2 * j + 1];
-    if (j < 2 * half) return x * cs[2 * (j - half)] + xs[i - half] * r * w[e - half] * cs[2 * (j - half) + 1];
+    const float r = i < nQ ? rq : rk;
+    const float x = xs[i] * r;
+    if (j < half) return x * cs[2 * j] - xs[i + half] * r * cs[2 * j + 1];
+    if (j < 2 * half) return x * cs[2 * (j - half)] + xs[i - half] * r * cs[2 * (j - half) + 1];
     return x;
   };
   TA* qd = q_out + (size_t)t * nQ;
   const int stop = slot < 0 ? nQ : n;  // a token without a slot stores nothing of k
-  if ((d & 1) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_dst & 7) == 0 && ((uintptr_t)v_dst & 7) == 0) {
+  if ((d & 1) == 0 && ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_dst & 7) == 0) {
     // a thread's place inside a head moves by the same amount every round: no division in the loop
     const int step = (blockDim.x * 2) % d;
     int j = (threadIdx.x * 2) % d;
@@ -151,9 +163,7 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
       if (i < nQ) {
         ts_store_pair(qd + i, a, b);
       } else {
-        const size_t at = (size_t)slot * nK + (i - nQ);
-        ts_store_pair(k_dst + at, a, b);
-        ts_store_pair(v_dst + at, xs[i], xs[i + 1]);  // the rows were read from this element type: exact
+        ts_store_pair(k_dst + (size_t)slot * nK + (i - nQ), a, b);
       }
     }
   } else {
@@ -162,9 +172,7 @@ __global__ void qk_joint_norm_rope_store_staged_kernel(const TA* __restrict__ qk
       if (i < nQ) {
         qd[i] = ts_from_float<TA>(a);
       } else {
-        const size_t at = (size_t)slot * nK + (i - nQ);
-        k_dst[at] = ts_from_float<TA>(a);
-        v_dst[at] = ts_from_float<TA>(xs[i]);
+        k_dst[(size_t)slot * nK + (i - nQ)] = ts_from_float<TA>(a);
       }
     }
   }
@@ -181,7 +189,8 @@ TS_EXPORT int ts_qk_joint_norm_rope_store(const void* qk, int act_dtype, long lo
   const size_t smem = (size_t)n * sizeof(float);
   if (smem <= 40 * 1024) {
     const size_t elem = act_dtype == TS_DTYPE_F32 ? 4 : 2;
-    const int wide = (n % 4 == 0 && (nq * d) % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qk % (4 * elem)) == 0) ? 1 : 0;
+    const int wide = (n % 4 == 0 && (nq * d) % 4 == 0 && ld % 4 == 0 && ((uintptr_t)qk % (4 * elem)) == 0 && ((uintptr_t)v_dst % (4 * elem)) == 0 &&
+                      (((uintptr_t)q_w | (uintptr_t)k_w) % 16) == 0) ? 1 : 0;
     // Few tokens: a row's pieces spread over many threads (shortest latency).  Many: smaller CTAs (16 entries a thread), so that
     // an SM holds more tokens at once and one token's load, reduction and store phases overlap with the others'.
     const int th = T >= 512 ? min(512, max(128, (n / 16 + 31) / 32 * 32)) : (wide ? min(512, max(64, (n / 4 + 31) / 32 * 32)) : threads);
