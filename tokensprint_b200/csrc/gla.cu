@@ -17,7 +17,9 @@
 // threads, then every thread runs the round's updates from there.
 // The state is read from the request's slot before the first token and written back after the
 // last, so a sequence may be cut anywhere, and a token's result depends on nothing but its own
-// sequence: the same sums in the same order whatever else is in the batch.
+// sequence: run in one piece, the same sums in the same order whatever else is in the batch (run
+// in segments, see below, the grouping of the sums follows the step's longest portion and the
+// number of sequences: float32 rounding, nothing else).
 // A sequence without tokens in this step (a padded lane of a fixed-size batch) touches nothing.
 #include "common.cuh"
 
